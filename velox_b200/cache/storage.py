@@ -28,7 +28,7 @@ class LayerCache:
 
     def num_bytes(self) -> int:
         total = 0
-        for t in (self.k, self.v, self.state):
+        for t in (self.k, None if self.v is self.k else self.v, self.state):
             if t is not None:
                 total += t.numel() * t.element_size()
         return total
@@ -47,7 +47,7 @@ def allocate_layer_cache(
     if needs.paged is not None:
         shape = (num_pages, page_size, needs.paged.num_kv_heads, needs.paged.head_dim)
         cache.k = torch.zeros(shape, dtype=dtype, device=device)
-        cache.v = torch.zeros(shape, dtype=dtype, device=device)
+        cache.v = cache.k if needs.paged.values_in_keys else torch.zeros(shape, dtype=dtype, device=device)
     if needs.state is not None:
         cache.state = torch.zeros(
             (max_num_seqs + 1,) + tuple(needs.state.shape), dtype=needs.state.dtype, device=device
@@ -61,7 +61,8 @@ def bytes_per_page(needs_list: List[CacheNeeds], page_size: int, dtype: torch.dt
     total = 0
     for needs in needs_list:
         if needs.paged is not None:
-            total += 2 * page_size * needs.paged.num_kv_heads * needs.paged.head_dim * element
+            arrays = 1 if needs.paged.values_in_keys else 2
+            total += arrays * page_size * needs.paged.num_kv_heads * needs.paged.head_dim * element
     return total
 
 

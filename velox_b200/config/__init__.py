@@ -1,5 +1,5 @@
 from .engine_config import EngineConfig, SchedulerConfig, resolve_dtype
-from .model_config import ConfigError, ModelConfig, Qwen2Config, read_config_json
+from .model_config import ConfigError, ModelConfig, PeratarConfig, Qwen2Config, read_config_json
 from .registry import (
     Architecture,
     architecture_of,
@@ -15,6 +15,7 @@ __all__ = [
     "ConfigError",
     "EngineConfig",
     "ModelConfig",
+    "PeratarConfig",
     "Qwen2Config",
     "SchedulerConfig",
     "architecture_of",

@@ -205,6 +205,160 @@ class Qwen2Config(ModelConfig):
         return out
 
 
+def _mapping(cfg: Mapping[str, Any], key: str, where: str) -> Mapping[str, Any]:
+    value = cfg.get(key)
+    if not isinstance(value, Mapping):
+        raise ConfigError(f"{where}: key {key!r} must be an object, got {value!r}")
+    return value
+
+
+def _number(cfg: Mapping[str, Any], key: str, where: str) -> float:
+    value = cfg.get(key)
+    if isinstance(value, bool) or not isinstance(value, (int, float)):
+        raise ConfigError(f"{where}: key {key!r} must be a number, got {value!r}")
+    return float(value)
+
+
+def _count(cfg: Mapping[str, Any], key: str, where: str) -> int:
+    value = cfg.get(key)
+    if isinstance(value, bool) or not isinstance(value, int) or value <= 0:
+        raise ConfigError(f"{where}: key {key!r} must be a positive integer, got {value!r}")
+    return value
+
+
+@dataclass(frozen=True)
+class LatentMixerConfig:
+    """One layer's latent attention: ``heads`` heads of ``dim`` unrotated and ``rot_dim`` rotated
+    query/key dims and ``vdim`` value dims over a cached latent of ``kv_rank`` values; pairs of
+    the first ``rot_dims`` rotated dims turn with ``rot_base``; ``kv_from`` names the layer whose
+    cached latent this layer reads instead of making its own."""
+
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot_base: float
+    rot_dims: int
+    kv_from: Optional[int] = None
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        out: Dict[str, Any] = {
+            "heads": self.heads, "dim": self.dim, "rot_dim": self.rot_dim, "vdim": self.vdim,
+            "kv_rank": self.kv_rank, "scale": self.scale,
+            "rot": {"base": self.rot_base, "dims": self.rot_dims},
+        }
+        if self.kv_from is not None:
+            out["kv_from"] = self.kv_from
+        return out
+
+
+@dataclass(frozen=True)
+class PeratarLayerConfig:
+    mixer: LatentMixerConfig
+    # Inner width of the dense feed-forward; None: the layer has none.
+    ff: Optional[int]
+
+
+@dataclass(frozen=True)
+class PeratarConfig(ModelConfig):
+    """``Peratar``: every layer is latent attention and, optionally, a dense xIELU feed-forward,
+    each followed by a gate, a weight-only layer norm and the residual add; a layer's input is
+    a learned weighted sum of the results of all layers before it.  config.json keys: ``vocab``,
+    ``width``, ``norm.eps``, ``logit_softcap`` and ``layers`` (a list of ``{type, mixer, mlp}``).
+    ``max_position_embeddings`` is optional (the design has no limit of its own)."""
+
+    layers: Tuple[PeratarLayerConfig, ...] = ()
+    norm_eps: float = 1e-5
+    logit_softcap: Optional[float] = None
+    torch_dtype: str = "bfloat16"
+
+    @staticmethod
+    def from_dict(cfg: Mapping[str, Any]) -> "PeratarConfig":
+        name = cfg.get("architecture") or (cfg.get("architectures") or ["Peratar"])[0]
+        raw_layers = cfg.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ConfigError("config.json key 'layers' must be a non-empty list")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"config.json layers[{index}]"
+            if not isinstance(raw, Mapping):
+                raise ConfigError(f"{where} must be an object")
+            kind = raw.get("type")
+            if kind != "latent_attention":
+                raise ConfigError(f"{where}: mixer type {kind!r} is not supported (only 'latent_attention' is)")
+            m = _mapping(raw, "mixer", where)
+            rot = _mapping(m, "rot", where + ".mixer")
+            kv_from = m.get("kv_from")
+            if kv_from is not None:
+                if isinstance(kv_from, bool) or not isinstance(kv_from, int) or not 0 <= kv_from < index:
+                    raise ConfigError(f"{where}: kv_from={kv_from!r} must name an earlier layer")
+            mixer = LatentMixerConfig(
+                heads=_count(m, "heads", where), dim=_count(m, "dim", where), rot_dim=_count(m, "rot_dim", where),
+                vdim=_count(m, "vdim", where), kv_rank=_count(m, "kv_rank", where),
+                scale=_number(m, "scale", where), rot_base=_number(rot, "base", where + ".mixer.rot"),
+                rot_dims=_count(rot, "dims", where + ".mixer.rot"), kv_from=kv_from,
+            )
+            if mixer.rot_dims % 2 or mixer.rot_dims > mixer.rot_dim:
+                raise ConfigError(f"{where}: rot.dims={mixer.rot_dims} must be even and at most rot_dim={mixer.rot_dim}")
+            if kv_from is not None:
+                source = layers[kv_from].mixer
+                if source.kv_from is not None:
+                    raise ConfigError(f"{where}: layer {kv_from} has no cached latent of its own to read")
+                if (source.kv_rank, source.rot_dim, source.rot_base, source.rot_dims) != (
+                        mixer.kv_rank, mixer.rot_dim, mixer.rot_base, mixer.rot_dims):
+                    raise ConfigError(f"{where}: kv_rank, rot_dim and rotation must equal those of layer {kv_from}")
+            mlp = raw.get("mlp")
+            ff = None
+            if mlp is not None:
+                if not isinstance(mlp, Mapping):
+                    raise ConfigError(f"{where}: key 'mlp' must be an object or null")
+                if mlp.get("kind") != "dense":
+                    raise ConfigError(f"{where}: mlp kind {mlp.get('kind')!r} is not supported (only 'dense' is)")
+                ff = _count(mlp, "ff", where + ".mlp")
+            layers.append(PeratarLayerConfig(mixer=mixer, ff=ff))
+        cap = cfg.get("logit_softcap")
+        if cap is not None and not float(cap) > 0.0:
+            raise ConfigError(f"logit_softcap must be positive, got {cap!r}")
+        eos = cfg.get("eos_token_id")
+        eos_ids: Tuple[int, ...] = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(t) for t in eos))
+        return PeratarConfig(
+            architecture=str(name),
+            vocab_size=_count(cfg, "vocab", "config.json"),
+            hidden_size=_count(cfg, "width", "config.json"),
+            num_hidden_layers=len(layers),
+            max_position_embeddings=int(cfg.get("max_position_embeddings", 1 << 20)),
+            tie_word_embeddings=False,
+            eos_token_ids=eos_ids,
+            layers=tuple(layers),
+            norm_eps=_number(_mapping(cfg, "norm", "config.json"), "eps", "config.json norm"),
+            logit_softcap=None if cap is None else float(cap),
+            torch_dtype=str(cfg.get("torch_dtype", "bfloat16")),
+        )
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        out: Dict[str, Any] = {
+            "architecture": self.architecture,
+            "vocab": self.vocab_size,
+            "width": self.hidden_size,
+            "norm": {"eps": self.norm_eps},
+            "layers": [
+                {"type": "latent_attention", "mixer": layer.mixer.to_json_dict(),
+                 "mlp": None if layer.ff is None else {"kind": "dense", "ff": layer.ff}}
+                for layer in self.layers
+            ],
+            "torch_dtype": self.torch_dtype,
+        }
+        if self.logit_softcap is not None:
+            out["logit_softcap"] = self.logit_softcap
+        if self.max_position_embeddings != 1 << 20:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out
+
+
 def read_config_json(model_dir: str) -> Dict[str, Any]:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):

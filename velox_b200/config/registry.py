@@ -50,9 +50,13 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(config_json: Mapping[str, Any]) -> Architecture:
     names = config_json.get("architectures")
-    if not names or not isinstance(names, (list, tuple)):
-        raise ConfigError("config.json has no 'architectures' list to choose the model by")
-    return get_architecture(str(names[0]))
+    if names and isinstance(names, (list, tuple)):
+        return get_architecture(str(names[0]))
+    # Some model folders name their one architecture with a plain string.
+    name = config_json.get("architecture")
+    if isinstance(name, str) and name:
+        return get_architecture(name)
+    raise ConfigError("config.json has neither an 'architectures' list nor an 'architecture' name to choose the model by")
 
 
 def load_model_config(model_dir: str) -> ModelConfig:

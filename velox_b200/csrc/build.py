@@ -34,7 +34,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo"]
 if os.environ.get("VELOX_B200_TRACE") == "1":
     COMMON_FLAGS = COMMON_FLAGS + ["-DVX_TRACE"]
 
-CORE_SOURCES = ("core.cu", "sampling.cu", "gemm_bf16.cu")
+CORE_SOURCES = ("core.cu", "sampling.cu", "gemm_bf16.cu", "residual.cu", "latent.cu")
 ATTENTION_SOURCES = ("attention.cu",)
 HEADERS = ("common.cuh", "attention_static.h")
 

@@ -1,0 +1,265 @@
+// Row-wise kernels for layers that normalise a sublayer's *result* before it joins the residual
+// stream, and for models that feed a layer a weighted sum of all earlier layers' results.
+//
+//   norm_rows_kernel        out[o] = norm(resid[r] + delta[r]) * w, layer norm (mean taken off,
+//                           variance = mean of squared deviations) or RMS norm, row selection
+//   gated_norm_add_kernel   y = delta * sigmoid(gate);  x += norm(y) * w;  optionally the
+//                           depth-weighted sum  sum_j mix[j] * X_j  over the kept results of all
+//                           layers so far, and a copy of the outgoing row in the compute dtype
+//                           for the projection that reads it next
+//   xielu_kernel            the two-branch quadratic / exponential activation
+//   softcap_kernel          cap * tanh(v / cap) on float32 logits
+//   cast_rows_kernel        float32 rows -> compute dtype
+//
+// Statistics, sigmoids, the residual sum and the depth-weighted sum are float32 whatever the
+// storage type.  Every sum has a fixed order that depends on the row length only, so a row's
+// result does not depend on what else is in the step.
+#include "common.cuh"
+
+namespace vx {
+
+constexpr int RN_MAX_PER_THREAD = 8;
+
+__device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// Mean (0 when `center` is off) and 1 / sqrt(mean((v - mean)^2) + eps) of a row given by
+// `value(i)`; two passes over the row, as the definition says.  `vals` caches the row when it
+// fits (hidden <= RN_MAX_PER_THREAD * blockDim.x).
+template <typename F>
+__device__ __forceinline__ void row_statistics(F value, int hidden, int center, float eps, bool cached,
+                                               float (&vals)[RN_MAX_PER_THREAD], float* scratch, float& mean,
+                                               float& inv) {
+  float s = 0.f;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < RN_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      vals[j] = i < hidden ? value(i) : 0.f;
+      s += vals[j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) s += value(i);
+  }
+  mean = 0.f;
+  if (center) mean = block_sum(s, scratch) / (float)hidden;
+  float ss = 0.f;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < RN_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      const float d = i < hidden ? vals[j] - mean : 0.f;
+      ss += d * d;
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = value(i) - mean;
+      ss += d * d;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[o] = norm(resid[r] + delta[r]) * weight, r = rows ? rows[o] : o.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void norm_rows_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                 const float* __restrict__ weight, float eps, int center, T* __restrict__ out,
+                                 const int* __restrict__ rows, int hidden, int write_resid) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* x = resid + (size_t)r * hidden;
+  const T* d = delta ? delta + (size_t)r * hidden : nullptr;
+  auto value = [&](int i) { return d ? x[i] + to_float(d[i]) : x[i]; };
+  const bool cached = hidden <= RN_MAX_PER_THREAD * (int)blockDim.x;
+  float vals[RN_MAX_PER_THREAD], mean, inv;
+  row_statistics(value, hidden, center, eps, cached, vals, scratch, mean, inv);
+  T* y = out + (size_t)o * hidden;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < RN_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < hidden) {
+        if (write_resid && d) x[i] = vals[j];
+        y[i] = from_float<T>((vals[j] - mean) * inv * weight[i]);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float v = value(i);
+      if (write_resid && d) x[i] = v;
+      y[i] = from_float<T>((v - mean) * inv * weight[i]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// A sublayer's result joins the stream:
+//   y        = delta[r] * sigmoid(gate[r])            (gate null: y = delta[r])
+//   x        = resid_in[r] + norm(y) * weight         -> resid_out[r]
+//   outgoing = x                                      (mix_terms == 0)
+//            = sum_{j < mix_terms - 1} mix_w[j] * hist[j][r]  +  mix_w[mix_terms - 1] * x
+//                                                      -> mix_out[r]
+//   lowp_out[r] = outgoing in the compute dtype (null: not written)
+// hist[j] = hist + j * hist_stride holds the kept rows of earlier results, [*, hidden] each.
+// resid_in may equal resid_out.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_norm_add_kernel(const float* resid_in, float* resid_out, const T* __restrict__ delta,
+                                      long long delta_ld, const T* __restrict__ gate, long long gate_ld,
+                                      const float* __restrict__ weight, float eps, int center,
+                                      T* __restrict__ lowp_out, const float* __restrict__ hist,
+                                      long long hist_stride, const float* __restrict__ mix_w, int mix_terms,
+                                      float* __restrict__ mix_out, int hidden) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const T* d = delta + (size_t)r * delta_ld;
+  const T* g = gate ? gate + (size_t)r * gate_ld : nullptr;
+  auto value = [&](int i) {
+    const float v = to_float(d[i]);
+    return g ? v * sigmoid_f32(to_float(g[i])) : v;
+  };
+  const bool cached = hidden <= RN_MAX_PER_THREAD * (int)blockDim.x;
+  float vals[RN_MAX_PER_THREAD], mean, inv;
+  row_statistics(value, hidden, center, eps, cached, vals, scratch, mean, inv);
+  const float* xin = resid_in + (size_t)r * hidden;
+  float* xout = resid_out + (size_t)r * hidden;
+  auto finish = [&](int i, float v) {
+    const float x = xin[i] + (v - mean) * inv * weight[i];
+    xout[i] = x;
+    float outgoing = x;
+    if (mix_terms > 0) {
+      float acc = 0.f;
+      for (int j = 0; j + 1 < mix_terms; ++j)
+        acc = fmaf(mix_w[j], hist[(size_t)j * hist_stride + (size_t)r * hidden + i], acc);
+      outgoing = fmaf(mix_w[mix_terms - 1], x, acc);
+      mix_out[(size_t)r * hidden + i] = outgoing;
+    }
+    if (lowp_out) lowp_out[(size_t)r * hidden + i] = from_float<T>(outgoing);
+  };
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < RN_MAX_PER_THREAD; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < hidden) finish(i, vals[j]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) finish(i, value(i));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// xIELU: z > 0: a_pos z^2 + z / 2;  z <= 0: a_neg (exp(z) - 1 - z) + z / 2, on [T, n] read with a
+// row pitch (the columns may be part of a wider projection) and written densely.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ in, long long in_ld, T* __restrict__ out, long long total,
+                             int n, float a_pos, float a_neg) {
+  allow_dependents();
+  grid_dependency_wait();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const long long t = idx / n;
+    const int i = (int)(idx - t * n);
+    const float z = to_float(in[t * in_ld + i]);
+    const float v = z > 0.f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+    out[idx] = from_float<T>(v);
+  }
+}
+
+__global__ void softcap_kernel(float* __restrict__ values, long long total, float cap) {
+  allow_dependents();
+  grid_dependency_wait();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride)
+    values[idx] = cap * tanhf(values[idx] / cap);
+}
+
+__global__ void cast_rows_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long long total) {
+  allow_dependents();
+  grid_dependency_wait();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride)
+    out[idx] = __float2bfloat16_rn(in[idx]);
+}
+
+static int row_threads(int hidden) {
+  int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
+  return threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+}
+
+static int flat_blocks(long long total, int threads) {
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return (int)blocks;
+}
+
+}  // namespace vx
+
+using namespace vx;
+
+VX_API int vx_norm_rows(float* resid, const void* delta, const float* weight, float eps, int center, void* out,
+                        int dtype, const int* rows, int num_out_rows, int hidden, int write_resid,
+                        cudaStream_t stream) {
+  if (num_out_rows <= 0) return 0;
+  const int threads = row_threads(hidden);
+  if (dtype == VX_DTYPE_F32)
+    launch_pdl(norm_rows_kernel<float>, dim3(num_out_rows), dim3(threads), 0, stream, resid, (const float*)delta,
+               weight, eps, center, (float*)out, rows, hidden, write_resid);
+  else
+    launch_pdl(norm_rows_kernel<__nv_bfloat16>, dim3(num_out_rows), dim3(threads), 0, stream, resid,
+               (const __nv_bfloat16*)delta, weight, eps, center, (__nv_bfloat16*)out, rows, hidden, write_resid);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_gated_norm_add(const float* resid_in, float* resid_out, const void* delta, long long delta_ld,
+                             const void* gate, long long gate_ld, const float* weight, float eps, int center,
+                             void* lowp_out, int dtype, const float* hist, long long hist_stride,
+                             const float* mix_w, int mix_terms, float* mix_out, int num_rows, int hidden,
+                             cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (mix_terms > 0 && (mix_w == nullptr || mix_out == nullptr || (mix_terms > 1 && hist == nullptr)))
+    return (int)cudaErrorInvalidValue;
+  const int threads = row_threads(hidden);
+  if (dtype == VX_DTYPE_F32)
+    launch_pdl(gated_norm_add_kernel<float>, dim3(num_rows), dim3(threads), 0, stream, resid_in, resid_out,
+               (const float*)delta, delta_ld, (const float*)gate, gate_ld, weight, eps, center, (float*)lowp_out,
+               hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
+  else
+    launch_pdl(gated_norm_add_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), 0, stream, resid_in, resid_out,
+               (const __nv_bfloat16*)delta, delta_ld, (const __nv_bfloat16*)gate, gate_ld, weight, eps, center,
+               (__nv_bfloat16*)lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_xielu(const void* in, long long in_ld, void* out, int dtype, int num_rows, int n, float a_pos,
+                    float a_neg, cudaStream_t stream) {
+  const long long total = (long long)num_rows * n;
+  if (total <= 0) return 0;
+  if (dtype == VX_DTYPE_F32)
+    launch_pdl(xielu_kernel<float>, dim3(flat_blocks(total, 256)), dim3(256), 0, stream, (const float*)in, in_ld,
+               (float*)out, total, n, a_pos, a_neg);
+  else
+    launch_pdl(xielu_kernel<__nv_bfloat16>, dim3(flat_blocks(total, 256)), dim3(256), 0, stream,
+               (const __nv_bfloat16*)in, in_ld, (__nv_bfloat16*)out, total, n, a_pos, a_neg);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_softcap(float* values, long long total, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+  launch_pdl(softcap_kernel, dim3(flat_blocks(total, 256)), dim3(256), 0, stream, values, total, cap);
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_cast_f32_to_bf16(const float* in, void* out, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  launch_pdl(cast_rows_kernel, dim3(flat_blocks(total, 256)), dim3(256), 0, stream, in, (__nv_bfloat16*)out, total);
+  return (int)cudaGetLastError();
+}

@@ -63,10 +63,15 @@ class CausalLM:
             mixer = mixer_cls(
                 layer.mixer.params, store.load_all(layer.mixer.weights), dtype, device, **mixer_extra
             )
-            feed_forward = _build("feed_forward", layer.feed_forward, store, dtype, device)
+            feed_forward = None
+            if layer.feed_forward is not None:
+                feed_forward = _build("feed_forward", layer.feed_forward, store, dtype, device)
             norms = {name: _build("norm", norm, store, dtype, device) for name, norm in layer.norms.items()}
             block_cls = part_class("block", layer.block)
-            self.blocks.append(block_cls(mixer, feed_forward, norms, layer.block_params))
+            block_extra = {}
+            if layer.block_weights:
+                block_extra = {"weights": store.load_all(layer.block_weights), "dtype": dtype, "device": device}
+            self.blocks.append(block_cls(mixer, feed_forward, norms, layer.block_params, **block_extra))
 
         # Cache groups: one per distinct need (all keys / a window) among the entries that own
         # a cache.  entry_group[i] is the group whose tables address entry i's pages.
@@ -116,7 +121,7 @@ class CausalLM:
         padded with tokens of no sequence (``takes_padded_steps``): only then are steps of any
         shape captured and replayed."""
         return all(getattr(part, "takes_padded_steps", False)
-                   for block in self.blocks for part in (block.mixer, block.feed_forward))
+                   for block in self.blocks for part in (block.mixer, block.feed_forward) if part is not None)
 
     def head_dims(self) -> List[int]:
         dims = []
@@ -129,10 +134,15 @@ class CausalLM:
     def forward(self, ctx, caches: List[LayerCache], input_ids, logit_rows, num_logit_rows: int):
         """Run the step's tokens through every schedule entry; logits (float32) at ``logit_rows``."""
         ws = ctx.workspace
-        resid = ws.get("model.resid", (ws.max_tokens, self.hidden_size), torch.float32)
+        # A block arrangement that keeps every layer's result has the stream start in its store.
+        home = getattr(self.blocks[self.spec.schedule[0].layer], "stream_home", None)
+        resid = home(ws) if home is not None else None
+        if resid is None:
+            resid = ws.get("model.resid", (ws.max_tokens, self.hidden_size), torch.float32)
         self.embedding.forward(input_ids, resid, ctx)
         hidden = HiddenState(resid=resid, delta=None)
         for index, entry in enumerate(self.spec.schedule):
+            ctx.entry_index = index
             self.blocks[entry.layer].forward(hidden, ctx, caches[index])
         if num_logit_rows == 0:
             return None

@@ -115,6 +115,11 @@ class StepContext:
     # int32 on the device, or None: the tokens the sampler drew in the step before, one per row.
     # A token id of -1 - r in this step's ids stands for row r of it (looked up by the embedding).
     fed_tokens: Optional[torch.Tensor] = None
+    # Which schedule entry is running (set by the model around every block).
+    entry_index: int = 0
+    # Columns of a part's first projection that belong to the block around it (a gate over the
+    # part's result): rows in the compute dtype, a view of the projection's output; None: none.
+    side_output: Optional[torch.Tensor] = None
     # Host copies, for parts that lay out work of their own.
     q_lens_host: List[int] = field(default_factory=list)
     kv_lens_host: List[int] = field(default_factory=list)

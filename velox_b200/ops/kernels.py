@@ -79,6 +79,21 @@ def core():
         lib.vx_gemm_bf16_normed.argtypes = [
             _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
+        lib.vx_norm_rows.argtypes = [_ptr, _ptr, _ptr, _c_f, _c_int, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr]
+        lib.vx_gated_norm_add.argtypes = [
+            _ptr, _ptr, _ptr, _c_ll, _ptr, _c_ll, _ptr, _c_f, _c_int, _ptr, _c_int, _ptr, _c_ll, _ptr, _c_int, _ptr,
+            _c_int, _c_int, _ptr,
+        ]
+        lib.vx_xielu.argtypes = [_ptr, _c_ll, _ptr, _c_int, _c_int, _c_int, _c_f, _c_f, _ptr]
+        lib.vx_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
+        lib.vx_cast_f32_to_bf16.argtypes = [_ptr, _ptr, _c_ll, _ptr]
+        lib.vx_latent_prepare.argtypes = [
+            _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _c_f, _ptr, _ptr, _c_ll,
+            _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr,
+        ]
+        lib.vx_headwise_linear.argtypes = [
+            _ptr, _c_ll, _c_int, _ptr, _ptr, _c_ll, _c_int, _ptr, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr,
+        ]
         lib.vx_gemm_bf16_qkv_rope.argtypes = [
             _ptr, _c_int, _ptr, _c_ll, _ptr, _c_f, _ptr, _ptr, _ptr, _c_int, _c_int, _c_ll, _c_int,
             _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _c_ll, _c_int, _c_int, _ptr, _ptr,
@@ -248,6 +263,232 @@ def add_rmsnorm(
                               1 if write_resid else 0, _stream()),
         "add_rmsnorm",
     )
+
+
+def norm_rows(
+    resid: torch.Tensor,
+    delta: Optional[torch.Tensor],
+    weight: torch.Tensor,
+    eps: float,
+    center: bool,
+    out: torch.Tensor,
+    num_rows: int,
+    rows: Optional[torch.Tensor] = None,
+    write_resid: bool = True,
+) -> None:
+    """v = resid + delta; resid = v (if write_resid); out = norm(v) * weight in float32, where
+    norm takes the mean off first when ``center`` is set (layer norm without bias) and divides
+    by sqrt(mean of squared deviations + eps).  ``rows`` as in ``add_rmsnorm``."""
+    _need(resid, torch.float32, "resid")
+    _need(weight, torch.float32, "weight")
+    _need(out, out.dtype, "out")
+    hidden = resid.shape[1]
+    if weight.numel() != hidden or out.shape[1] != hidden:
+        raise ValueError("norm weight / output width does not match the residual width")
+    if delta is not None:
+        _need(delta, out.dtype, "delta")
+        if delta.shape[1] != hidden:
+            raise ValueError("delta width does not match the residual width")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        if rows.numel() < num_rows:
+            raise ValueError(f"{num_rows} rows asked for, the index array names {rows.numel()}")
+    elif resid.shape[0] < num_rows or (delta is not None and delta.shape[0] < num_rows):
+        raise ValueError(f"{num_rows} rows asked for, the input has {resid.shape[0]}")
+    if out.shape[0] < num_rows:
+        raise ValueError(f"{num_rows} rows asked for, the output holds {out.shape[0]}")
+    _check(
+        core().vx_norm_rows(_p(resid), _p(delta), _p(weight), float(eps), 1 if center else 0, _p(out),
+                            _code(out.dtype), _p(rows), num_rows, hidden, 1 if write_resid else 0, _stream()),
+        "norm_rows",
+    )
+
+
+def _rows_view(t: torch.Tensor, name: str, dtype: torch.dtype, num_rows: int, width: int) -> int:
+    """Checks a [rows, >= width] view with unit column stride; returns its row pitch."""
+    if t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.shape[1] < width or t.shape[0] < num_rows:
+        raise ValueError(f"{name} must be device rows [>= {num_rows}, >= {width}] with unit column stride, "
+                         f"got {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+def gated_norm_add(
+    resid_in: torch.Tensor,
+    resid_out: torch.Tensor,
+    delta: torch.Tensor,
+    gate: Optional[torch.Tensor],
+    weight: torch.Tensor,
+    eps: float,
+    center: bool,
+    num_rows: int,
+    lowp_out: Optional[torch.Tensor] = None,
+    history: Optional[torch.Tensor] = None,
+    mix_weights: Optional[torch.Tensor] = None,
+    mix_out: Optional[torch.Tensor] = None,
+) -> None:
+    """A sublayer's result joins the float32 stream: ``y = delta * sigmoid(gate)`` (``gate``
+    None: ``y = delta``), ``resid_out = resid_in + norm(y) * weight``.  ``delta`` and ``gate``
+    are rows in the compute dtype and may be column ranges of wider buffers.
+
+    With ``mix_weights`` (float32 [n]) what goes on is ``sum_{j < n-1} mix_weights[j] *
+    history[j] + mix_weights[n-1] * resid_out`` (``history`` float32 [>= n-1, rows, width]: the
+    kept results of earlier layers), written to ``mix_out``.  ``lowp_out`` gets what goes on
+    (the mixed rows, or ``resid_out`` without a mix) in the compute dtype."""
+    _need(resid_in, torch.float32, "resid_in")
+    _need(resid_out, torch.float32, "resid_out")
+    _need(weight, torch.float32, "weight")
+    hidden = resid_in.shape[1]
+    if resid_out.shape[1] != hidden or weight.numel() != hidden:
+        raise ValueError("gated_norm_add: widths do not agree")
+    if resid_in.shape[0] < num_rows or resid_out.shape[0] < num_rows:
+        raise ValueError(f"gated_norm_add: {num_rows} rows asked for")
+    dtype = delta.dtype
+    delta_ld = _rows_view(delta, "delta", dtype, num_rows, hidden)
+    gate_ld = 0 if gate is None else _rows_view(gate, "gate", dtype, num_rows, hidden)
+    if lowp_out is not None:
+        _need(lowp_out, dtype, "lowp_out")
+        if lowp_out.shape[1] != hidden or lowp_out.shape[0] < num_rows:
+            raise ValueError("gated_norm_add: lowp_out does not hold the rows")
+    terms, hist_stride = 0, 0
+    if mix_weights is not None:
+        _need(mix_weights, torch.float32, "mix_weights")
+        terms = mix_weights.numel()
+        if mix_out is None:
+            raise ValueError("gated_norm_add: a mix needs mix_out")
+        _need(mix_out, torch.float32, "mix_out")
+        if mix_out.shape[1] != hidden or mix_out.shape[0] < num_rows:
+            raise ValueError("gated_norm_add: mix_out does not hold the rows")
+        if terms > 1:
+            _need(history, torch.float32, "history")
+            if history.dim() != 3 or history.shape[0] < terms - 1 or history.shape[1] < num_rows or history.shape[2] != hidden:
+                raise ValueError(f"gated_norm_add: history {tuple(history.shape)} does not hold {terms - 1} results")
+            hist_stride = history.stride(0)
+    _check(
+        core().vx_gated_norm_add(_p(resid_in), _p(resid_out), _p(delta), delta_ld, _p(gate), gate_ld, _p(weight),
+                                 float(eps), 1 if center else 0, _p(lowp_out), _code(dtype), _p(history), hist_stride,
+                                 _p(mix_weights), terms, _p(mix_out), num_rows, hidden, _stream()),
+        "gated_norm_add",
+    )
+
+
+def xielu(x: torch.Tensor, out: torch.Tensor, num_rows: int, a_pos: float, a_neg: float) -> None:
+    """out[t, i] = a_pos z^2 + z / 2 for z = x[t, i] > 0, else a_neg (exp(z) - 1 - z) + z / 2;
+    ``x`` may be a column range of a wider buffer, ``out`` is dense [rows, n]."""
+    _need(out, out.dtype, "out")
+    n = out.shape[1]
+    ld = _rows_view(x, "x", out.dtype, num_rows, n)
+    if out.shape[0] < num_rows:
+        raise ValueError("xielu: out does not hold the rows")
+    _check(core().vx_xielu(_p(x), ld, _p(out), _code(out.dtype), num_rows, n, float(a_pos), float(a_neg), _stream()),
+           "xielu")
+
+
+def softcap(values: torch.Tensor, num_rows: int, cap: float) -> None:
+    """values[:num_rows] = cap * tanh(values / cap), in place (float32)."""
+    _need(values, torch.float32, "values")
+    _check(core().vx_softcap(_p(values), num_rows * values.shape[1], float(cap), _stream()), "softcap")
+
+
+def cast_f32_to_bf16(src: torch.Tensor, out: torch.Tensor, count: int) -> None:
+    _need(src, torch.float32, "src")
+    _need(out, torch.bfloat16, "out")
+    _check(core().vx_cast_f32_to_bf16(_p(src), _p(out), count, _stream()), "cast")
+
+
+def latent_prepare(
+    proj: torch.Tensor,
+    q_offset: int,
+    latent_offset: Optional[int],
+    positions: torch.Tensor,
+    cos: torch.Tensor,
+    sin: torch.Tensor,
+    latent_weight: Optional[torch.Tensor],
+    eps: float,
+    slots: Optional[torch.Tensor],
+    cache: Optional[torch.Tensor],
+    queries: torch.Tensor,
+    num_tokens: int,
+    num_heads: int,
+    dim: int,
+    rot_dim: int,
+    kv_rank: int,
+    status: torch.Tensor,
+) -> None:
+    """What a latent-attention layer does to its projections before attention (latent.cu).
+
+    ``proj`` [T, width]: head h's query at ``q_offset + h * (dim + rot_dim)``, its last
+    ``rot_dim`` dims rotate; the token's latent (``kv_rank`` values) and shared key part
+    (``rot_dim`` values) at ``latent_offset`` (None: the layer reads another layer's cache).
+    ``queries`` [T, heads, D]: dims ``kv_rank ...`` get the rotated parts and zero padding.
+    ``cache`` [pages, page, 1, D]: the token's row at ``slots[t]`` gets [rms-normed latent |
+    rotated key part | zeros]; a negative slot writes nothing."""
+    dtype = proj.dtype
+    _need(proj, dtype, "proj")
+    _need(queries, dtype, "queries")
+    _need(positions, torch.int32, "positions")
+    _need(cos, torch.float32, "cos")
+    _need(sin, torch.float32, "sin")
+    padded = queries.shape[-1]
+    if queries.numel() < num_tokens * num_heads * padded or proj.shape[0] < num_tokens:
+        raise ValueError("latent_prepare: buffers do not hold the tokens")
+    write = latent_offset is not None
+    num_slots = 0
+    if write:
+        _need(cache, dtype, "cache")
+        _need(slots, torch.int32, "slots")
+        _need(latent_weight, torch.float32, "latent_weight")
+        if cache.shape[-1] != padded or cache.shape[2] != 1 or latent_weight.numel() != kv_rank:
+            raise ValueError("latent_prepare: cache rows or norm weight do not match the sizes")
+        num_slots = cache.shape[0] * cache.shape[1]
+    _check(
+        core().vx_latent_prepare(_p(proj), proj.stride(0), int(q_offset), int(latent_offset) if write else -1,
+                                 _code(dtype), _p(positions), _p(cos), _p(sin), cos.shape[0], cos.shape[1],
+                                 _p(latent_weight) if write else None, float(eps), _p(slots) if write else None,
+                                 _p(cache) if write else None, num_slots, _p(queries), num_tokens, num_heads, dim,
+                                 rot_dim, kv_rank, padded, _p(status), _stream()),
+        "latent_prepare",
+    )
+
+
+def headwise_linear(
+    x: torch.Tensor,
+    x_offset: int,
+    x_head_stride: int,
+    weight: torch.Tensor,
+    out: torch.Tensor,
+    out_offset: int,
+    out_head_stride: int,
+    num_tokens: int,
+    gate: Optional[torch.Tensor] = None,
+    gate_offset: int = 0,
+) -> None:
+    """out[t, out_offset + h * out_head_stride + n] = sum_k weight[h, n, k] * x[t, x_offset + h *
+    x_head_stride + k], times sigmoid(gate[t, gate_offset + h]) with a gate.  ``x``, ``out`` and
+    ``gate`` are dense 2-D buffers in the dtype of ``weight`` [heads, N, K]; float32 sums."""
+    dtype = weight.dtype
+    _need(weight, dtype, "weight")
+    _need(x, dtype, "x")
+    _need(out, dtype, "out")
+    heads, n, k = weight.shape
+    if x_offset + (heads - 1) * x_head_stride + k > x.shape[1] or out_offset + (heads - 1) * out_head_stride + n > out.shape[1]:
+        raise ValueError("headwise_linear: the heads do not fit the rows")
+    if x.shape[0] < num_tokens or out.shape[0] < num_tokens:
+        raise ValueError("headwise_linear: buffers do not hold the tokens")
+    gate_ptr, gate_ld = None, 0
+    if gate is not None:
+        _need(gate, dtype, "gate")
+        if gate_offset + heads > gate.shape[1]:
+            raise ValueError("headwise_linear: the gate columns do not fit the rows")
+        gate_ptr, gate_ld = gate.data_ptr() + gate_offset * gate.element_size(), gate.stride(0)
+    code = core().vx_headwise_linear(x.data_ptr() + x_offset * x.element_size(), x.stride(0), x_head_stride,
+                                     _p(weight), out.data_ptr() + out_offset * out.element_size(), out.stride(0),
+                                     out_head_stride, gate_ptr, gate_ld, _code(dtype), num_tokens, heads, n, k,
+                                     _stream())
+    if code == -1:
+        raise KernelError(f"headwise_linear refuses an inner size of {k}")
+    _check(code, "headwise_linear")
 
 
 def rope_cache_write(

@@ -52,6 +52,9 @@ class PagedCacheSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    # The cached rows serve as keys and as values (a cached latent): no value pages exist and
+    # ``LayerCache.v`` is ``LayerCache.k``.
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)
@@ -141,6 +144,9 @@ class FeedForward(Part):
 
 
 class Norm(Part):
+    # Whether the mean is taken off before the division (layer norm) or not (RMS norm).
+    center = False
+
     def forward(self, resid, delta, out, num_rows, rows=None, write_resid=True) -> torch.Tensor:  # pragma: no cover
         raise NotImplementedError
 
@@ -160,3 +166,6 @@ class HiddenState:
 
     resid: torch.Tensor
     delta: Optional[torch.Tensor] = None
+    # The rows of ``resid`` in the compute dtype, when the kernel that made them wrote that copy
+    # too (valid only while ``delta`` is None); a block that has none makes its own.
+    lowp: Optional[torch.Tensor] = None

@@ -10,6 +10,7 @@ import os
 
 import torch
 
+from ..ops import kernels
 from .base import HiddenState
 from .registry import register_part
 
@@ -58,3 +59,96 @@ class PreNormBlock:
                 return pending
         norm.forward(resid, delta, out, num_rows)
         return out
+
+
+@register_part("block", "post_norm")
+class PostNormBlock:
+    """The norm sits on each sublayer's result, not on its input:
+
+        x <- x + norm_mixer(gate_1 * mixer(x));   x <- x + norm_ff(gate_2 * feed_forward(x))
+
+    The sublayers read the stream itself (in the compute dtype).  ``gate_k = sigmoid(W x + b)``
+    element by element when the part hands over side columns of its first projection
+    (``ctx.side_output``: the block's W rides along as extra rows of that projection), else 1.
+    A layer may have no feed-forward.
+
+    ``depth_mix``: what goes on to the next layer is not the layer's result X_(e+1) but
+    ``sum_{j <= e+1} w[j] X_j`` over the results of all layers so far (X_0 the embedding output),
+    with the layer's own weights ``depth_mix.weight`` [e + 2].  The results are kept in one
+    float32 store [entries + 2, tokens, width]: slot e + 1 is the layer's working copy of the
+    stream (it starts as the layer's input and ends as X_(e+1)), the mixed rows go to slot e + 2,
+    which is the next layer's working copy.  Each sublayer's gate, norm, add (and the mix after
+    the last one) is one kernel, which also writes the outgoing rows in the compute dtype for
+    the projection that reads them next.
+    """
+
+    def __init__(self, mixer, feed_forward, norms, params=None, weights=None, dtype=None, device=None) -> None:
+        params = dict(params or {})
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norm_mixer = norms["mixer"]
+        self.norm_feed_forward = norms.get("feed_forward")
+        if feed_forward is not None and self.norm_feed_forward is None:
+            raise ValueError("a post_norm block with a feed-forward needs its norm")
+        self.depth_mix = bool(params.get("depth_mix", False))
+        self.num_entries = int(params.get("num_entries", 0))
+        self.mix_weight = None
+        if self.depth_mix:
+            if weights is None or "depth_mix.weight" not in weights:
+                raise ValueError("a block with depth_mix needs the weight 'depth_mix.weight'")
+            if self.num_entries < 1:
+                raise ValueError("a block with depth_mix needs num_entries (the schedule's length)")
+            self.mix_weight = weights["depth_mix.weight"]
+
+    def _store(self, ws, width):
+        return ws.get("block.results", (self.num_entries + 2, ws.max_tokens, width), torch.float32)
+
+    def stream_home(self, ws):
+        """Where the embedding output belongs: slot 0 of the store of results (None: anywhere)."""
+        if not self.depth_mix:
+            return None
+        return self._store(ws, self.norm_mixer.size)[0]
+
+    def forward(self, hidden: HiddenState, ctx, cache) -> None:
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        width = hidden.resid.shape[1]
+        dtype = self.mixer.dtype
+        if hidden.delta is not None:
+            raise ValueError("a post_norm block takes a stream with nothing pending")
+        x_in = hidden.resid
+        work, store, mix_out, entry = x_in, None, None, ctx.entry_index
+        if self.depth_mix:
+            if self.mix_weight.numel() != entry + 2:
+                raise ValueError(f"schedule entry {entry} mixes {entry + 2} results, its weight has {self.mix_weight.numel()}")
+            store = self._store(ws, width)
+            work, mix_out = store[entry + 1], store[entry + 2]
+        lowp = None
+        if dtype != torch.float32:
+            lowp = ws.get("block.lowp", (ws.max_tokens, width), dtype)
+            if hidden.lowp is None:
+                kernels.cast_f32_to_bf16(x_in, lowp, T * width)
+        source = x_in if lowp is None else lowp
+
+        ctx.residual = None
+        ctx.side_output = None
+        mixed = self.mixer.forward(source, ctx, cache)
+        last = self.feed_forward is None
+        self._join(x_in, work, mixed, ctx.side_output, self.norm_mixer, T, lowp, store, mix_out, last)
+        if not last:
+            source = work if lowp is None else lowp
+            ctx.side_output = None
+            product = self.feed_forward.forward(source, ctx)
+            self._join(work, work, product, ctx.side_output, self.norm_feed_forward, T, lowp, store, mix_out, True)
+        ctx.side_output = None
+        hidden.resid = mix_out if self.depth_mix else work
+        hidden.delta = None
+        hidden.lowp = lowp
+
+    def _join(self, resid_in, resid_out, delta, gate, norm, num_rows, lowp, store, mix_out, last) -> None:
+        mixing = self.depth_mix and last
+        kernels.gated_norm_add(
+            resid_in, resid_out, delta, gate, norm.weight, norm.eps, norm.center, num_rows, lowp_out=lowp,
+            history=store if mixing else None, mix_weights=self.mix_weight if mixing else None,
+            mix_out=mix_out if mixing else None,
+        )

@@ -27,15 +27,26 @@ class TokenEmbedding(Part):
 
 @register_part("lm_head", "linear_head")
 class LinearHead(Part):
-    """``logits = x @ W.T`` without bias, returned in float32."""
+    """``logits = x @ W.T`` without bias, returned in float32; with a ``softcap`` parameter c the
+    logits become ``c * tanh(logits / c)``."""
 
     def __init__(self, params, weights, dtype, device) -> None:
         super().__init__(params, weights, dtype, device)
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
         self.weight = self.expect("weight", (self.vocab_size, self.hidden_size))
+        cap = params.get("softcap")
+        self.softcap = None if cap is None else float(cap)
+        if self.softcap is not None and not self.softcap > 0.0:
+            raise ValueError(f"softcap must be positive, got {self.softcap}")
 
     def forward(self, x, num_rows, ctx) -> torch.Tensor:
+        logits = self._project(x, num_rows, ctx)
+        if self.softcap is not None:
+            kernels.softcap(logits, num_rows, self.softcap)
+        return logits
+
+    def _project(self, x, num_rows, ctx) -> torch.Tensor:
         ws = ctx.workspace
         logits = ws.get("lm_head.logits", (ws.max_logit_rows, self.vocab_size), torch.float32)
         if self.dtype == torch.float32:

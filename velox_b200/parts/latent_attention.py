@@ -1,0 +1,136 @@
+"""Attention over a cached low-rank latent.
+
+Per token the layer caches one row: a latent ``c`` of ``kv_rank`` values (the first rows of the
+down projection, RMS-normed) and one rotated key part of ``rot_dim`` values that all heads
+share.  Head h's key is ``[W_uk[h] c | k_rot]`` and its value ``W_uv[h] c``; queries are laid out
+head by head as ``[dim unrotated | rot_dim rotated]``.  Because the unrotated score
+``q_u . (W_uk[h] c)`` equals ``(W_uk[h]^T q_u) . c``, the step never expands keys or values:
+
+    proj  = [W_q ; W_dkv ; W_g ; side rows] x            one projection of the layer's input
+    c, k_rot -> cache;  q_rot rotated                    kernels.latent_prepare
+    q_abs[h] = W_uk[h]^T q_u[h]                          kernels.headwise_linear
+    o_lat[h] = softmax(([q_abs[h] | q_rot[h]] . [c | k_rot]) * scale) applied to the rows c
+                                                         the paged attention kernels, one shared
+                                                         KV head whose rows are keys and values
+    o[h]     = sigmoid(g[h]) * W_uv[h] o_lat[h]          kernels.headwise_linear with the gate
+    out      = W_o o
+
+A layer with ``own_latent`` false has no down projection: it reads the cache of the schedule entry
+named by the model's schedule (``cache.read_only``) with its own W_uk, W_uv and queries.
+
+``side_rows`` > 0: the last rows of ``in.weight`` are not the mixer's; their products (plus
+``side.bias``) belong to the block around it and are handed over as ``ctx.side_output``.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import linear
+from .base import CacheNeeds, Mixer, PagedCacheSpec
+from .registry import register_part
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    takes_padded_steps = True
+
+    def __init__(self, params, weights, dtype, device, position=None) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.hidden_size = int(params["hidden_size"])
+        self.num_heads = int(params["num_heads"])
+        self.dim = int(params["dim"])
+        self.rot_dim = int(params["rot_dim"])
+        self.value_dim = int(params["value_dim"])
+        self.kv_rank = int(params["kv_rank"])
+        self.softmax_scale = float(params["softmax_scale"])
+        self.eps = float(params["eps"])
+        self.own_latent = bool(params.get("own_latent", True))
+        self.gated = bool(params.get("output_gate", True))
+        self.side_rows = int(params.get("side_rows", 0))
+        if position is None or not hasattr(position, "pairs"):
+            raise ValueError("latent attention needs a pair-rotating position encoding part")
+        if 2 * position.pairs > self.rot_dim:
+            raise ValueError(f"the rotation covers {2 * position.pairs} dims, the rotated part has {self.rot_dim}")
+        self.position = position
+        # A cached row, padded to what the attention kernels take (a multiple of 16 up to 256).
+        self.row_dim = -(-(self.kv_rank + self.rot_dim) // 16) * 16
+        if self.row_dim > 256:
+            raise ValueError(
+                f"kv_rank + rot_dim = {self.kv_rank + self.rot_dim} is more than the attention kernels' "
+                "largest row of 256"
+            )
+        H, q_head = self.num_heads, self.dim + self.rot_dim
+        self.q_width = H * q_head
+        self.latent_offset = self.q_width
+        self.gate_offset = self.q_width + (self.kv_rank + self.rot_dim if self.own_latent else 0)
+        self.side_offset = self.gate_offset + (H if self.gated else 0)
+        self.in_width = self.side_offset + self.side_rows
+        self.w_in = self.expect("in.weight", (self.in_width, self.hidden_size))
+        self.b_in = None
+        self.b_in_lowp = None
+        if self.side_rows and "side.bias" in weights:
+            side = self.expect("side.bias", (self.side_rows,))
+            self.b_in = torch.cat([torch.zeros(self.side_offset, dtype=torch.float32, device=side.device), side])
+            self.b_in = self.b_in.contiguous()
+            if dtype != torch.float32:
+                self.b_in_lowp = self.b_in.to(dtype)
+        self.latent_norm = self.expect("latent_norm.weight", (self.kv_rank,)) if self.own_latent else None
+        # W_uk [H * dim, kv_rank] is used transposed per head (the contraction runs over dim).
+        w_uk = self.expect("uk.weight", (H * self.dim, self.kv_rank))
+        self.w_uk_t = w_uk.view(H, self.dim, self.kv_rank).transpose(1, 2).contiguous()
+        self.w_uv = self.expect("uv.weight", (H * self.value_dim, self.kv_rank)).view(H, self.value_dim, self.kv_rank)
+        self.w_out = self.expect("out.weight", (self.hidden_size, H * self.value_dim))
+        kernels.attention_lib(self.row_dim)
+
+    def cache_needs(self) -> CacheNeeds:
+        return CacheNeeds(paged=PagedCacheSpec(1, self.row_dim, None, values_in_keys=True))
+
+    def attention_signature(self):
+        return (1, self.num_heads, None, self.row_dim)
+
+    def forward(self, x, ctx, cache):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        H, Dp = self.num_heads, self.row_dim
+        if cache.read_only == self.own_latent:
+            raise ValueError("a latent-attention layer writes the cache exactly when it has a down projection")
+        proj = ws.get(f"latent.proj{self.in_width}", (ws.max_tokens, self.in_width), self.dtype)
+        linear(x, self.w_in, self.b_in, proj, T, self.b_in_lowp, status=ctx.status)
+        ctx.side_output = proj[:, self.side_offset:] if self.side_rows else None
+
+        queries = ws.get("latent.queries", (ws.max_tokens, H * Dp), self.dtype)
+        group = ctx.groups[cache.group]
+        kernels.latent_prepare(
+            proj, 0, self.latent_offset if self.own_latent else None, ctx.positions, self.position.cos,
+            self.position.sin, self.latent_norm, self.eps, group.slot_mapping, cache.k,
+            queries.view(ws.max_tokens, H, Dp), T, H, self.dim, self.rot_dim, self.kv_rank, ctx.status,
+        )
+        kernels.headwise_linear(proj, 0, self.dim + self.rot_dim, self.w_uk_t, queries, 0, Dp, T)
+
+        attn = ws.get("latent.attn", (ws.max_tokens, H * Dp), self.dtype)
+        plan = ctx.attention_plan(cache.group, self.attention_signature())
+        for kind, items, count in plan.launches:
+            kernels.attention(
+                kind, queries, attn, cache.k, cache.k, group.block_tables, ctx.q_start, ctx.q_len,
+                ctx.kv_len, items, count, plan.partial_o, plan.partial_lse, H, 1, Dp, None,
+                self.softmax_scale, merge_items=plan.merge_items, split_counters=plan.split_counters,
+                status=ctx.status,
+                cluster=(plan.cluster if kind == kernels.ATTN_BF16_NARROW else
+                         getattr(plan, "tc_ctas_per_sm", 1) if kind == kernels.ATTN_BF16_TC else 1),
+                layout_checked=getattr(plan, "checked", False),
+            )
+        if hasattr(plan, "checked"):
+            plan.checked = True
+        if plan.num_merges and plan.split_counters is None:
+            kernels.attention_merge(
+                attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o, plan.partial_lse,
+                H, 1, Dp, max_rows=plan.merge_rows,
+            )
+
+        heads_out = ws.get("latent.heads", (ws.max_tokens, H * self.value_dim), self.dtype)
+        kernels.headwise_linear(attn, 0, Dp, self.w_uv, heads_out, 0, self.value_dim, T,
+                                gate=proj if self.gated else None, gate_offset=self.gate_offset)
+        out = ws.get("mixer.out", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(heads_out, self.w_out, None, out, T, status=ctx.status)
+        return out

@@ -4,6 +4,7 @@ with gate and up fused into one matrix whose first half is gate, and no biases
 rounds to the model dtype between the two)."""
 from __future__ import annotations
 
+import math
 import os
 
 import torch
@@ -66,4 +67,50 @@ class SwiGLU(FeedForward):
         kernels.swiglu(gate_up, act, T)
         out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(act, self.w_down, None, out, T)
+        return out
+
+
+def _softplus(value: float) -> float:
+    return max(value, 0.0) + math.log1p(math.exp(-abs(value)))
+
+
+@register_part("feed_forward", "dense_xielu")
+class DenseXielu(FeedForward):
+    """``down(act(up(x)))`` with biases on both projections and the xIELU activation with two
+    learned numbers p, q (``act`` weight): ``z > 0: softplus(p) z^2 + z / 2``, ``z <= 0:
+    (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``, computed in float32.
+
+    ``side_rows`` > 0: the last rows of ``up.weight`` / ``up.bias`` are not the feed-forward's;
+    their products belong to the block around it (a gate over the result) and are handed over
+    as ``ctx.side_output``, so the block's projection of the same input rides along."""
+
+    takes_padded_steps = True
+
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.hidden_size = int(params["hidden_size"])
+        self.intermediate_size = int(params["intermediate_size"])
+        self.side_rows = int(params.get("side_rows", 0))
+        rows = self.intermediate_size + self.side_rows
+        self.w_up = self.expect("up.weight", (rows, self.hidden_size))
+        self.b_up = self.expect("up.bias", (rows,))
+        self.w_down = self.expect("down.weight", (self.hidden_size, self.intermediate_size))
+        self.b_down = self.expect("down.bias", (self.hidden_size,))
+        self.b_up_lowp = self.b_up.to(dtype) if dtype != torch.float32 else None
+        self.b_down_lowp = self.b_down.to(dtype) if dtype != torch.float32 else None
+        p, q = (float(v) for v in self.expect("act", (2,)).tolist())
+        self.a_pos = _softplus(p)
+        self.a_neg = 0.5 + _softplus(q)
+
+    def forward(self, x, ctx):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        rows = self.intermediate_size + self.side_rows
+        up = ws.get("dense.up", (ws.max_tokens, rows), self.dtype)
+        linear(x, self.w_up, self.b_up, up, T, self.b_up_lowp, status=ctx.status)
+        ctx.side_output = up[:, self.intermediate_size:] if self.side_rows else None
+        act = ws.get("dense.act", (ws.max_tokens, self.intermediate_size), self.dtype)
+        kernels.xielu(up, act, T, self.a_pos, self.a_neg)
+        out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(act, self.w_down, self.b_down, out, T, self.b_down_lowp, status=ctx.status)
         return out

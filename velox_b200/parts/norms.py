@@ -23,3 +23,21 @@ class RMSNorm(Norm):
 
     def pending(self, resid, out, num_rows):
         return PendingNorm(self, resid, out, num_rows)
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(Norm):
+    """Layer norm with a weight and no bias: ``out = (v - mean(v)) / sqrt(var(v) + eps) * weight``
+    where ``var`` is the mean of the squared deviations, ``v = resid + delta``, in float32."""
+
+    center = True
+
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.weight = self.expect("weight", (self.size,))
+
+    def forward(self, resid, delta, out, num_rows, rows=None, write_resid=True):
+        kernels.norm_rows(resid, delta, self.weight, self.eps, True, out, num_rows, rows, write_resid)
+        return out

@@ -60,3 +60,32 @@ class NoPosition(PositionEncoding):
             qkv, ctx.positions, None, None, slots, k_cache, v_cache, ctx.num_tokens,
             num_heads, num_kv_heads, self.head_dim, 0, ctx.status,
         )
+
+
+@register_part("position", "rotary_interleaved")
+class RotaryInterleaved(PositionEncoding):
+    """Rotation of neighbouring pairs: dims ``2i`` and ``2i + 1`` of the first ``rotary_dim`` dims
+    of a vector are a pair ``(u, v) -> (u cos a - v sin a, v cos a + u sin a)`` with ``a =
+    position * base^(-2i / rotary_dim)``; the other dims pass.  The part owns the float32 tables
+    ``cos``/``sin`` [max_position, rotary_dim / 2] (angles formed in float64, rounded once); the
+    mixer that applies it passes them to its kernel."""
+
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.rotary_dim = int(params["rotary_dim"])
+        self.base = float(params["base"])
+        self.max_position = int(params["max_position"])
+        if self.rotary_dim % 2 != 0 or self.rotary_dim < 0:
+            raise ValueError(f"rotary_dim={self.rotary_dim} must be even")
+        pairs = self.rotary_dim // 2
+        exponent = torch.arange(pairs, dtype=torch.float64) * (2.0 / max(self.rotary_dim, 1))
+        inv_freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), -exponent)
+        angles = torch.outer(torch.arange(self.max_position, dtype=torch.float64), inv_freq)
+        width = max(pairs, 1)
+        cos = torch.ones((self.max_position, width), dtype=torch.float32)
+        sin = torch.zeros((self.max_position, width), dtype=torch.float32)
+        cos[:, :pairs] = angles.cos().to(torch.float32)
+        sin[:, :pairs] = angles.sin().to(torch.float32)
+        self.pairs = pairs
+        self.cos = cos.to(device).contiguous()
+        self.sin = sin.to(device).contiguous()

@@ -56,11 +56,14 @@ class LayerSpec:
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    # None: the layer has no feed-forward (its block arrangement must allow that).
+    feed_forward: Optional[PartSpec]
     norms: Dict[str, PartSpec]
     # Position encoding the mixer applies; None for a mixer that needs none.
     position: Optional[PartSpec] = None
     block_params: Dict[str, Any] = field(default_factory=dict)
+    # Weights of the arrangement itself (the weights of a sum over earlier layers, say).
+    block_weights: Dict[str, WeightSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -95,8 +98,11 @@ class ModelSpec:
         out: List[PartSpec] = [self.embedding]
         for layer in self.layers:
             out.append(layer.mixer)
-            out.append(layer.feed_forward)
+            if layer.feed_forward is not None:
+                out.append(layer.feed_forward)
             out.extend(layer.norms.values())
+            if layer.block_weights:
+                out.append(PartSpec(kind=layer.block, weights=layer.block_weights))
             if layer.position is not None:
                 out.append(layer.position)
         out.extend([self.final_norm, self.lm_head])

@@ -7,7 +7,8 @@ checkpoint (src/weight_loader.py:139-155).
 
 Every tensor is drawn from its own generator, keyed by (seed, tensor name), so a tensor's
 values do not depend on which other tensors exist or on the order they are made in.  Matrices
-and biases are N(0, std); norm weights are 1 + N(0, std) so that a missing norm multiply shows.
+and biases are N(0, std); norm weights are 1 + N(0, std) so that a missing norm multiply shows;
+the weights of a weighted sum are 1/n + N(0, std).
 """
 from __future__ import annotations
 
@@ -42,6 +43,9 @@ def random_tensor(source: TensorSource, seed: int, std: float, dtype: torch.dtyp
     values.normal_(0.0, std, generator=generator)
     if source.init == "one_plus_normal":
         values += 1.0
+    elif source.init == "average_plus_normal":
+        # Weights of a sum over the tensor's entries that keeps the scale of what it sums.
+        values += 1.0 / max(values.numel(), 1)
     elif source.init != "normal":
         raise ValueError(f"unknown init {source.init!r} for {source.name}")
     return values.to(dtype)
