@@ -42,7 +42,8 @@ BF16_MIN_COSINE = 0.999
 BF16_MIN_ARGMAX_AGREEMENT = 0.95
 
 
-def check_logits(got_rows, want_rows, dtype: str, what: str, f32_tolerance: float = F32_TOLERANCE) -> None:
+def check_logits(got_rows, want_rows, dtype: str, what: str, f32_tolerance: float = F32_TOLERANCE,
+                 bf16_tolerance: float = BF16_TOLERANCE, bf16_min_cosine: float = BF16_MIN_COSINE) -> None:
     """Engine logits against the plain implementation's (float64), row by row.
 
     float32: both sides round differently in sums of a few hundred to a few thousand terms; the
@@ -73,11 +74,11 @@ def check_logits(got_rows, want_rows, dtype: str, what: str, f32_tolerance: floa
     row_scale = want.abs().amax(-1).clamp_min(1e-3)
     ratio = err / row_scale
     worst_row = int(ratio.argmax())
-    assert ratio[worst_row].item() <= BF16_TOLERANCE, (
+    assert ratio[worst_row].item() <= bf16_tolerance, (
         f"{what}: row {worst_row}: max abs error {err[worst_row].item():.3e}, its largest logit {row_scale[worst_row].item():.3e}")
     cosine = torch.nn.functional.cosine_similarity(got, want, dim=-1)
-    assert cosine.min().item() >= BF16_MIN_COSINE, f"{what}: row {int(cosine.argmin())}: cosine {cosine.min().item():.5f}"
-    clear = gap > BF16_TOLERANCE * row_scale
+    assert cosine.min().item() >= bf16_min_cosine, f"{what}: row {int(cosine.argmin())}: cosine {cosine.min().item():.5f}"
+    clear = gap > bf16_tolerance * row_scale
     if int(clear.sum()) > 0:
         agreement = same[clear].double().mean().item()
         assert agreement >= BF16_MIN_ARGMAX_AGREEMENT, f"{what}: argmax agrees in {agreement:.3f} of {int(clear.sum())} clear rows"

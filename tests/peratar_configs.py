@@ -1,0 +1,102 @@
+"""Small Peratar configurations and weights for the tests.
+
+The configurations differ in every size; some make sizes differ that a model may happen to make
+equal (the rotated width and the number of dims that rotate, the sizes of different layers), have
+a layer without feed-forward, a single head, cached rows that need padding, inner sizes that
+are no multiple of eight.  ``make_weights`` draws weights at a scale at which the model does
+something (a unit-variance stream, gates away from 1/2) and can sharpen the attention so that a
+key that is lost or wrongly seen changes the logits visibly.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Dict, Optional
+
+import torch
+
+
+def mixer(heads, dim, rot_dim, vdim, kv_rank, scale, base=10000.0, rot_dims=None, kv_from=None) -> Dict[str, Any]:
+    out = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": scale,
+           "rot": {"base": base, "dims": rot_dim if rot_dims is None else rot_dims}}
+    if kv_from is not None:
+        out["kv_from"] = kv_from
+    return out
+
+
+def layer(mix, ff: Optional[int]) -> Dict[str, Any]:
+    return {"type": "latent_attention", "mixer": mix, "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+
+
+def config(width, vocab, layers, eps=1e-5, cap=12.0) -> Dict[str, Any]:
+    return {"architecture": "Peratar", "vocab": vocab, "width": width, "norm": {"eps": eps},
+            "logit_softcap": cap, "layers": layers}
+
+
+# Three layers, the middle one without feed-forward, the last one on the first one's cache.
+SMALL = config(96, 200, [
+    layer(mixer(3, 16, 8, 24, 40, 0.21, base=500.0), 72),
+    layer(mixer(3, 16, 8, 24, 40, 0.21, base=500.0), None),
+    layer(mixer(2, 24, 8, 16, 40, 0.18, base=500.0, kv_from=0), 56),
+], eps=1e-6, cap=9.0)
+
+# Every layer another size: one head; a rotated part of which only some dims rotate; cached rows
+# of 32, 39 (padded to 48) and 16 values; a rank and inner widths that are no multiple of eight;
+# two layers reading other layers' caches.
+ODD = config(128, 331, [
+    layer(mixer(1, 8, 12, 8, 20, 0.3, base=10000.0, rot_dims=8), 100),
+    layer(mixer(5, 24, 6, 16, 33, 0.17, base=77.0), 132),
+    layer(mixer(2, 16, 6, 40, 33, 0.25, base=77.0, kv_from=1), None),
+    layer(mixer(4, 8, 4, 8, 12, 0.35, base=3.0e5), 64),
+    layer(mixer(3, 40, 12, 8, 20, 0.11, base=10000.0, rot_dims=8, kv_from=0), 60),
+], eps=1e-5, cap=30.0)
+
+# Cached rows of 128 values and eight heads: the shapes for which prompt portions run on the
+# tensor-memory attention kernel and decoded tokens on clusters; unrotated, rotated and value
+# widths all equal.
+WIDE = config(256, 500, [
+    layer(mixer(8, 32, 32, 32, 96, 0.125, base=250000.0), 512),
+    layer(mixer(8, 32, 32, 32, 96, 0.125, base=250000.0, kv_from=0), 512),
+], eps=1e-5, cap=15.0)
+
+ALL = {"small": SMALL, "odd": ODD, "wide": WIDE}
+
+
+def make_weights(cfg: Dict[str, Any], seed: int, sharp: float = 1.0) -> Dict[str, torch.Tensor]:
+    """bfloat16 tensors under the checkpoint's names.  ``sharp`` scales the query projections: at
+    4 or more the softmax puts most of its weight on a few keys, wherever they are."""
+    from velox_b200.config.registry import architecture_of
+
+    arch = architecture_of(cfg)
+    spec = arch.build_spec(arch.parse_config(cfg))
+    gen = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, source in sorted(spec.checkpoint_tensors().items()):
+        shape = tuple(source.shape)
+        if name == "embed":
+            t = torch.randn(shape, generator=gen)
+        elif name.endswith("norm") or name.endswith("norm1") or name.endswith("norm2"):
+            t = 1.0 + 0.3 * torch.randn(shape, generator=gen)
+        elif name.endswith(".dwa"):
+            t = torch.full(shape, 1.0 / shape[0]) + 0.3 * torch.randn(shape, generator=gen)
+        elif name.endswith(".act"):
+            t = torch.randn(shape, generator=gen)
+        elif len(shape) == 1:
+            t = 0.5 * torch.randn(shape, generator=gen)
+        else:
+            t = torch.randn(shape, generator=gen) / shape[1] ** 0.5
+            if name.endswith("mix.q"):
+                t = t * sharp
+            if name.endswith("mix.uk"):
+                t = t * 2.0
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+def write_folder(folder: str, cfg: Dict[str, Any], tensors: Dict[str, torch.Tensor]) -> None:
+    from safetensors.torch import save_file
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as handle:
+        json.dump(cfg, handle)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, os.path.join(folder, "model.safetensors"))

@@ -95,11 +95,13 @@ class LatentAttention(Mixer):
         H, Dp = self.num_heads, self.row_dim
         if cache.read_only == self.own_latent:
             raise ValueError("a latent-attention layer writes the cache exactly when it has a down projection")
+        # Buffers are named by their width: layers of different sizes must not take turns
+        # reallocating one name (a captured step keeps the addresses it was captured with).
         proj = ws.get(f"latent.proj{self.in_width}", (ws.max_tokens, self.in_width), self.dtype)
         linear(x, self.w_in, self.b_in, proj, T, self.b_in_lowp, status=ctx.status)
         ctx.side_output = proj[:, self.side_offset:] if self.side_rows else None
 
-        queries = ws.get("latent.queries", (ws.max_tokens, H * Dp), self.dtype)
+        queries = ws.get(f"latent.queries{H * Dp}", (ws.max_tokens, H * Dp), self.dtype)
         group = ctx.groups[cache.group]
         kernels.latent_prepare(
             proj, 0, self.latent_offset if self.own_latent else None, ctx.positions, self.position.cos,
@@ -108,7 +110,7 @@ class LatentAttention(Mixer):
         )
         kernels.headwise_linear(proj, 0, self.dim + self.rot_dim, self.w_uk_t, queries, 0, Dp, T)
 
-        attn = ws.get("latent.attn", (ws.max_tokens, H * Dp), self.dtype)
+        attn = ws.get(f"latent.attn{H * Dp}", (ws.max_tokens, H * Dp), self.dtype)
         plan = ctx.attention_plan(cache.group, self.attention_signature())
         for kind, items, count in plan.launches:
             kernels.attention(
@@ -128,7 +130,7 @@ class LatentAttention(Mixer):
                 H, 1, Dp, max_rows=plan.merge_rows,
             )
 
-        heads_out = ws.get("latent.heads", (ws.max_tokens, H * self.value_dim), self.dtype)
+        heads_out = ws.get(f"latent.heads{H * self.value_dim}", (ws.max_tokens, H * self.value_dim), self.dtype)
         kernels.headwise_linear(attn, 0, Dp, self.w_uv, heads_out, 0, self.value_dim, T,
                                 gate=proj if self.gated else None, gate_offset=self.gate_offset)
         out = ws.get("mixer.out", (ws.max_tokens, self.hidden_size), self.dtype)

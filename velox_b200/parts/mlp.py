@@ -106,10 +106,10 @@ class DenseXielu(FeedForward):
         T = ctx.num_tokens
         ws = ctx.workspace
         rows = self.intermediate_size + self.side_rows
-        up = ws.get("dense.up", (ws.max_tokens, rows), self.dtype)
+        up = ws.get(f"dense.up{rows}", (ws.max_tokens, rows), self.dtype)
         linear(x, self.w_up, self.b_up, up, T, self.b_up_lowp, status=ctx.status)
         ctx.side_output = up[:, self.intermediate_size:] if self.side_rows else None
-        act = ws.get("dense.act", (ws.max_tokens, self.intermediate_size), self.dtype)
+        act = ws.get(f"dense.act{self.intermediate_size}", (ws.max_tokens, self.intermediate_size), self.dtype)
         kernels.xielu(up, act, T, self.a_pos, self.a_neg)
         out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(act, self.w_down, self.b_down, out, T, self.b_down_lowp, status=ctx.status)
