@@ -2,6 +2,7 @@
 tokens/s at 2,048 tokens, at Qwen2.5-1.5B layer sizes with random weights, on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py --compare-designs 0.5b,1.5b     (another workload: see ``run_compare``)
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second of the step function (device time
 of K decode steps queued back to back, CUDA events; each step is fed the tokens the step
@@ -633,6 +634,60 @@ def _reference_numbers(args, ref_root):
     }
 
 
+def run_compare(args):
+    """``--compare-designs SIZE,...``: one layer of the Peratar design beside one layer of the
+    Qwen2 design at the same width, head count and feed-forward weight count (the presets
+    ``peratar-<size>`` and ``<size>`` of ``velox_b200.config.presets``), random weights.  Per
+    design and size: the time of a decode layer (``--batch`` requests behind 4,096 keys) against
+    its bytes and the measured copy bandwidth, the time of a 2,048-token prompt layer against its
+    operations and the measured library bf16 rate, and the time a layer spends in every kind of
+    launch.  A layer's time is the difference of a 6-layer and a 2-layer model over four, so
+    embedding, head and the host's share cancel (the vocabulary is cut to 8,192 for that reason).
+    Prints one JSON line."""
+    from velox_b200.cli import roofline
+    from velox_b200.config.presets import model_size
+
+    peaks = load_peaks()
+    options = argparse.Namespace(block_size=args.block_size, steps=args.steps, warmup=args.warmup)
+    few, many = 2, 6
+    rows = []
+    for size in args.compare_designs.split(","):
+        for name in (size, "peratar-" + size):
+            cfg = model_size(name)
+            cfg["vocab" if "vocab" in cfg else "vocab_size"] = 8192
+            cfg.pop("tie_word_embeddings", None)
+            keys = CONTEXT - args.steps - args.warmup - 2
+            short = roofline.step_times(cfg, few, [args.batch], [keys], options)[(args.batch, keys)]
+            long = roofline.step_times(cfg, many, [args.batch], [keys], options)[(args.batch, keys)]
+            decode_s = (long - short) / (many - few) * 1e-3
+            weights, cached = roofline.layer_bytes(cfg, args.batch, keys + args.warmup + args.steps // 2)
+            short = roofline.portion_times(cfg, few, [PREFILL_TOKENS], [0], options)[(PREFILL_TOKENS, 0)]
+            long = roofline.portion_times(cfg, many, [PREFILL_TOKENS], [0], options)[(PREFILL_TOKENS, 0)]
+            prefill_s = (long - short) / (many - few) * 1e-3
+            flops = roofline.layer_flops(cfg, PREFILL_TOKENS, 0)
+            row = {
+                "design": "Peratar" if name.startswith("peratar-") else "Qwen2", "size": size,
+                "decode": {"batch": args.batch, "keys": keys, "us_per_layer": round(decode_s * 1e6, 1),
+                           "layer_bytes": weights + cached, "us_by_bytes": round((weights + cached) / (peaks["hbm_gbs"] * 1e9) * 1e6, 1),
+                           "hbm_frac": round((weights + cached) / decode_s / 1e9 / peaks["hbm_gbs"], 3),
+                           "tokens_per_s_per_layer": round(args.batch / decode_s, 1)},
+                "prefill": {"tokens": PREFILL_TOKENS, "us_per_layer": round(prefill_s * 1e6, 1),
+                            "tflops": round(flops / prefill_s / 1e12, 1),
+                            "bf16_frac": round(flops / prefill_s / 1e12 / peaks["bf16_tflops"], 3),
+                            "tokens_per_s_per_layer": round(PREFILL_TOKENS / prefill_s, 1)},
+            }
+            if args.points:
+                row["decode"]["launches_us"] = roofline.layer_launch_times(cfg, few, many, options, batch=args.batch, context=keys)
+                row["prefill"]["launches_us"] = roofline.layer_launch_times(cfg, few, many, options, tokens=PREFILL_TOKENS)
+            rows.append(row)
+            print(f"[bench] {row['design']} {size}: decode {row['decode']['us_per_layer']} us/layer, "
+                  f"prefill {row['prefill']['us_per_layer']} us/layer", file=sys.stderr, flush=True)
+    print(json.dumps({"metric": "time of one layer, decode and prefill, two designs at equal sizes", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "peaks": peaks,
+                      "data": "synthetic: seeded random weights", "kv_block_size": args.block_size, "rows": rows}))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -643,6 +698,9 @@ def main():
     parser.add_argument("--block-size", type=int, default=BLOCK_SIZE, help="keys per cache page of the main engine (reported)")
     parser.add_argument("--impl", default="own", choices=["own", "reference"])
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 / 64 points")
+    parser.add_argument("--compare-designs", default=None, metavar="SIZE,...",
+                        help="instead of the benchmark: one layer of the Peratar design beside one of the Qwen2 design "
+                             "at the named sizes (0.5b, 1.5b, 3b, 7b), decode and prefill")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 or world > 1:
@@ -651,6 +709,8 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.compare_designs:
+        return run_compare(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_own(args)

@@ -83,8 +83,8 @@ def test_spec_names_shapes_and_schedule():
     assert "l2.mlp.up" not in tensors and "l2.norm2" not in tensors and "l2.rg2" not in tensors
     assert [entry.cache_of for entry in spec.schedule] == [None, None, 1, None, 0]
     mixer = spec.layers[1].mixer
-    assert [s.name for s in mixer.weights["in.weight"].sources] == ["l1.mix.q", "l1.mix.dkv", "l1.mix.g", "l1.rg1"]
-    assert [s.name for s in spec.layers[2].mixer.weights["in.weight"].sources] == ["l2.mix.q", "l2.mix.g", "l2.rg1"]
+    assert [s.name for s in mixer.weights["in.weight"].sources] == ["l1.rg1", "l1.mix.q", "l1.mix.dkv", "l1.mix.g"]
+    assert [s.name for s in spec.layers[2].mixer.weights["in.weight"].sources] == ["l2.rg1", "l2.mix.q", "l2.mix.g"]
     assert spec.lm_head.params["softcap"] == 30.0
 
 

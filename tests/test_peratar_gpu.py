@@ -113,6 +113,29 @@ def test_xielu_and_softcap(dtype):
     close(logits, want, "float32", "soft cap")
 
 
+@pytest.mark.parametrize("tokens,side,inner,width", [(1, 0, 72, 64), (9, 64, 200, 64), (100, 128, 330, 128), (256, 8, 64, 256)])
+def test_projection_with_activation_in_its_epilogue(tokens, side, inner, width):
+    """The tensor-core projection that writes its first columns as they are and the others through
+    the activation into a second buffer, against the two steps made plainly."""
+    from velox_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(tokens + inner)
+    x = torch.randn(tokens + 3, width, generator=gen).to(torch.bfloat16).cuda()
+    w = (2 * torch.randn(side + inner, width, generator=gen) / width ** 0.5).to(torch.bfloat16).cuda()
+    bias = torch.randn(side + inner, generator=gen).cuda()
+    out = torch.zeros(tokens + 3, side + inner + 8, dtype=torch.bfloat16).cuda()
+    act = torch.zeros(tokens + 3, inner, dtype=torch.bfloat16).cuda()
+    status = torch.zeros(4, dtype=torch.int32).cuda()
+    p, q = -0.2, 0.9
+    assert kernels.gemm_bf16_xielu(x, w, bias, out, act, side, plain.softplus(p), 0.5 + plain.softplus(q), tokens, status)
+    assert int(status[0]) == 0
+    full = x[:tokens].double() @ w.double().T + bias.double()
+    if side:
+        close(out[:tokens, :side], full[:, :side], "bfloat16", "columns that pass")
+    close(act[:tokens], plain.xielu(full[:, side:].cpu(), p, q), "bfloat16", "activated columns")
+    assert torch.all(act[tokens:] == 0) and torch.all(out[:, side:] == 0)
+
+
 @pytest.mark.parametrize("dtype", list(DTYPES))
 @pytest.mark.parametrize("heads,dim,rot,rot_dims,rank", [(3, 16, 8, 8, 40), (1, 8, 12, 8, 20), (5, 24, 6, 6, 33)])
 def test_latent_prepare(dtype, heads, dim, rot, rot_dims, rank):

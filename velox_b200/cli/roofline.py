@@ -45,9 +45,29 @@ def parse_args(argv: Optional[List[str]] = None) -> argparse.Namespace:
     return parser.parse_args(argv)
 
 
+def _latent_layers(config_json: Dict) -> Optional[List[Dict]]:
+    """The per-layer entries of a configuration that lists its layers (latent attention and a
+    dense feed-forward with gates), or None for a configuration of uniform Qwen2 layers."""
+    return config_json.get("layers")
+
+
 def layer_bytes(config_json: Dict, batch: int, context: int) -> Tuple[int, int]:
-    """(bytes of one layer's matrices in bfloat16, bytes of ``batch`` x ``context`` keys and
-    values of one layer)."""
+    """(bytes of one layer's matrices in bfloat16, bytes of ``batch`` x ``context`` cached rows of
+    one layer: keys and values, or the latent rows that serve as both), averaged over the layers
+    of a configuration that lists them."""
+    entries = _latent_layers(config_json)
+    if entries is not None:
+        width = config_json["width"]
+        weights = cache = 0
+        for entry in entries:
+            m = entry["mixer"]
+            heads, q_head, row = m["heads"], m["dim"] + m["rot_dim"], m["kv_rank"] + m["rot_dim"]
+            rows_in = heads * q_head + heads + width + (row if m.get("kv_from") is None else 0)
+            weights += 2 * (rows_in * width + heads * (m["dim"] + m["vdim"]) * m["kv_rank"] + width * heads * m["vdim"])
+            if entry.get("mlp") is not None:
+                weights += 2 * ((entry["mlp"]["ff"] + width) * width + width * entry["mlp"]["ff"])
+            cache += batch * context * (-(-row // 16) * 16) * 2
+        return weights // len(entries), cache // len(entries)
     width, heads, kv_heads = config_json["hidden_size"], config_json["num_attention_heads"], config_json["num_key_value_heads"]
     inner = config_json["intermediate_size"]
     head_dim = config_json.get("head_dim") or width // heads
@@ -57,12 +77,93 @@ def layer_bytes(config_json: Dict, batch: int, context: int) -> Tuple[int, int]:
 
 
 def layer_flops(config_json: Dict, tokens: int, context: int) -> float:
-    """Floating-point operations of one layer on a portion of ``tokens`` behind ``context`` keys."""
+    """Floating-point operations of one layer on a portion of ``tokens`` behind ``context`` keys
+    (for latent attention: as the engine computes it, scores and sums over the cached rows)."""
+    entries = _latent_layers(config_json)
+    pairs = tokens * (context + (tokens + 1) / 2.0)
+    if entries is not None:
+        weights, _ = layer_bytes(config_json, 0, 0)
+        attention = 0.0
+        for entry in entries:
+            m = entry["mixer"]
+            attention += 2.0 * pairs * m["heads"] * (2 * m["kv_rank"] + m["rot_dim"])
+        return 2.0 * tokens * (weights / 2) + attention / len(entries)
     width, heads, kv_heads = config_json["hidden_size"], config_json["num_attention_heads"], config_json["num_key_value_heads"]
     inner = config_json["intermediate_size"]
     head_dim = config_json.get("head_dim") or width // heads
     weights = width * (heads + 2 * kv_heads) * head_dim + heads * head_dim * width + 3 * width * inner
-    return 2.0 * tokens * weights + 4.0 * tokens * (context + (tokens + 1) / 2.0) * heads * head_dim
+    return 2.0 * tokens * weights + 4.0 * pairs * heads * head_dim
+
+
+def launch_times(config_json: Dict, layers: int, args, batch: int = 0, tokens: int = 0, context: int = 0,
+                 repeats: int = 5) -> Dict[str, float]:
+    """Microseconds of every kind of launch, summed over one step of a model of ``layers`` layers
+    (``batch`` single tokens behind ``context`` keys each, or one portion of ``tokens``): the step
+    is launched kernel by kernel behind a queued delay with a CUDA event after every launch
+    (``ops.kernels.launch_events``); the median over ``repeats`` steps."""
+    import torch
+
+    from ..config import EngineConfig
+    from ..config.presets import with_layers
+    from ..engine.engine import Engine
+    from ..engine.runner import StepChunk
+    from ..ops import kernels
+    from ..weights import write_random_model
+
+    seqs_n, per_seq = (batch, 1) if batch else (1, tokens)
+    most_keys = context + per_seq + 8
+    with tempfile.TemporaryDirectory(prefix="velox_roofline_") as folder:
+        write_random_model(folder, with_layers(config_json, layers), seed=0, dtype="bfloat16")
+        engine = Engine.from_pretrained(EngineConfig(
+            model=folder, dtype="bfloat16", max_model_len=most_keys, max_num_seqs=max(seqs_n, 2),
+            max_num_batched_tokens=max(256, per_seq, seqs_n), max_prefill_chunk_size=max(256, per_seq),
+            block_size=args.block_size, num_gpu_blocks=max(seqs_n, 2) * (-(-most_keys // args.block_size) + 1) + 8,
+            seed=0, enable_cuda_graphs=False))
+    runner, cache = engine.runner, engine.cache
+    seqs = []
+    for index in range(seqs_n):
+        seq = cache.new_sequence(f"k{index}")
+        if not (cache.acquire_slot(seq) and cache.append_slots(seq, context + per_seq)):
+            raise RuntimeError(f"the pool does not hold {seqs_n} sequences of {context + per_seq} keys")
+        cache.advance(seq, context)
+        seqs.append(seq)
+    chunks = [StepChunk(seq, [1 + (i % 97) for i in range(per_seq)], (per_seq - 1,)) for seq in seqs]
+    runs = []
+    for _ in range(repeats + 2):
+        ctx, ids, rows, count = runner.prepare(chunks)
+        torch.cuda.synchronize()
+        torch.cuda._sleep(40_000_000)
+        first = torch.cuda.Event(enable_timing=True)
+        first.record()
+        kernels.launch_events = []
+        try:
+            runner.model.forward(ctx, runner.layer_caches, ids, rows, count)
+        finally:
+            events, kernels.launch_events = kernels.launch_events, None
+        torch.cuda.synchronize()
+        took, previous = [], first
+        for name, event in events:
+            took.append((name, previous.elapsed_time(event) * 1000.0))
+            previous = event
+        runs.append(took)
+    runs = runs[2:]
+    out: Dict[str, float] = {}
+    for index, (name, _) in enumerate(runs[0]):
+        values = sorted(run[index][1] for run in runs)
+        out[name] = out.get(name, 0.0) + values[len(values) // 2]
+    runner.check_status()
+    del engine, runner, cache
+    torch.cuda.empty_cache()
+    return out
+
+
+def layer_launch_times(config_json: Dict, few: int, many: int, args, **step) -> Dict[str, float]:
+    """Microseconds one layer spends in every kind of launch: ``launch_times`` of a model of
+    ``many`` layers minus that of one of ``few``, over the difference (what is outside the layers
+    cancels)."""
+    short = launch_times(config_json, few, args, **step)
+    long = launch_times(config_json, many, args, **step)
+    return {name: round((long[name] - short.get(name, 0.0)) / (many - few), 2) for name in long}
 
 
 def portion_times(config_json: Dict, layers: int, portions: List[int], contexts: List[int], args) -> Dict[Tuple[int, int], float]:
@@ -72,11 +173,12 @@ def portion_times(config_json: Dict, layers: int, portions: List[int], contexts:
     from ..config import EngineConfig
     from ..engine.engine import Engine
     from ..engine.runner import StepChunk
+    from ..config.presets import with_layers
     from ..weights import write_random_model
 
     most_tokens, most_keys = max(portions), max(contexts) + max(portions) + 8
     with tempfile.TemporaryDirectory(prefix="velox_roofline_") as folder:
-        write_random_model(folder, dict(config_json, num_hidden_layers=layers), seed=0, dtype="bfloat16")
+        write_random_model(folder, with_layers(config_json, layers), seed=0, dtype="bfloat16")
         engine = Engine.from_pretrained(EngineConfig(
             model=folder, dtype="bfloat16", max_model_len=most_keys, max_num_seqs=2,
             max_num_batched_tokens=most_tokens, max_prefill_chunk_size=most_tokens, block_size=args.block_size,
@@ -117,11 +219,12 @@ def step_times(config_json: Dict, layers: int, batches: List[int], contexts: Lis
     from ..engine.engine import Engine
     from ..engine.runner import StepChunk
     from ..sampling.params import SamplingParams
+    from ..config.presets import with_layers
     from ..weights import write_random_model
 
     most_seqs, most_keys = max(batches), max(contexts) + args.steps + args.warmup + 2
     with tempfile.TemporaryDirectory(prefix="velox_roofline_") as folder:
-        write_random_model(folder, dict(config_json, num_hidden_layers=layers), seed=0, dtype="bfloat16")
+        write_random_model(folder, with_layers(config_json, layers), seed=0, dtype="bfloat16")
         engine = Engine.from_pretrained(EngineConfig(
             model=folder, dtype="bfloat16", max_model_len=most_keys, max_num_seqs=most_seqs,
             max_num_batched_tokens=max(256, most_seqs), max_prefill_chunk_size=256, block_size=args.block_size,

@@ -1,4 +1,5 @@
-"""Named example configurations of the Qwen2.5 dense family, as ``config.json`` dictionaries.
+"""Named example configurations of the Qwen2.5 dense family, and of the Peratar design at the same
+widths, as ``config.json`` dictionaries.
 
 They exist for runs with random weights (``--model-size`` of the benchmark command line): no
 checkpoint is needed to time the layer sizes of a published model.  Nothing in the engine
@@ -7,6 +8,7 @@ those of the published Qwen2.5 checkpoints (0.5B ... 14B) and of two tiny test s
 """
 from __future__ import annotations
 
+import copy
 from typing import Any, Dict
 
 
@@ -35,9 +37,57 @@ MODEL_SIZES: Dict[str, Dict[str, Any]] = {
 }
 
 
+def _peratar(like: str, rot_dim: int = 32, kv_rank: int = 96, share_every: int = 2) -> Dict[str, Any]:
+    """A Peratar configuration with the width, head count, layer count and vocabulary of the named
+    Qwen2.5 size: query heads as wide as that model's (``rot_dim`` of their dims rotate), values as
+    wide as its heads, a latent of ``kv_rank`` values, every ``share_every``-th layer reading the
+    cache of the layer before it, and a dense inner width that gives a layer (gates included)
+    as many weights in its feed-forward as the gated feed-forward of that size has."""
+    base = MODEL_SIZES[like]
+    width, heads, layers = base["hidden_size"], base["num_attention_heads"], base["num_hidden_layers"]
+    head = base.get("head_dim") or width // heads
+    inner = max(64, (3 * base["intermediate_size"] - 2 * width) // 2 // 64 * 64)
+    entries = []
+    for index in range(layers):
+        mixer = {"heads": heads, "dim": head - rot_dim, "rot_dim": rot_dim, "vdim": head, "kv_rank": kv_rank,
+                 "scale": (head ** -0.5), "rot": {"base": base["rope_theta"], "dims": rot_dim}}
+        if share_every > 1 and index % share_every == share_every - 1:
+            mixer["kv_from"] = index - 1
+        entries.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": inner}})
+    return {"architecture": "Peratar", "vocab": base["vocab_size"], "width": width, "norm": {"eps": 1e-5},
+            "logit_softcap": 30.0, "layers": entries, "max_position_embeddings": base["max_position_embeddings"]}
+
+
+MODEL_SIZES.update({
+    "peratar-0.5b": _peratar("0.5b"),
+    "peratar-1.5b": _peratar("1.5b"),
+    "peratar-3b": _peratar("3b"),
+    "peratar-7b": _peratar("7b"),
+})
+
+
+def with_layers(config_json: Dict[str, Any], layers: int) -> Dict[str, Any]:
+    """The configuration with another number of layers of the same sizes (a list of layers is cut,
+    or repeated from its start with every ``kv_from`` kept at its distance)."""
+    out = copy.deepcopy(config_json)
+    if "layers" not in out:
+        out["num_hidden_layers"] = layers
+        return out
+    given = out["layers"]
+    entries = []
+    for index in range(layers):
+        entry = copy.deepcopy(given[index % len(given)])
+        source = entry["mixer"].get("kv_from")
+        if source is not None:
+            entry["mixer"]["kv_from"] = index - (index % len(given) - source)
+        entries.append(entry)
+    out["layers"] = entries
+    return out
+
+
 def model_size(name: str) -> Dict[str, Any]:
     """A copy of the named configuration; KeyError lists the names."""
     try:
-        return dict(MODEL_SIZES[name])
+        return copy.deepcopy(MODEL_SIZES[name])
     except KeyError:
         raise KeyError(f"unknown model size {name!r}; known: {', '.join(sorted(MODEL_SIZES))}") from None

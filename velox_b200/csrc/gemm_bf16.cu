@@ -37,6 +37,9 @@
 //   2  out f32   [T, ldy] += acc                (projection added straight into the float32
 //                                                residual stream; one CTA owns each element;
 //                                                optionally the sums go to a second buffer too)
+//   5  out bf16  [T, ldy] = acc + bias for columns below a bound, xIELU(acc + bias) of the others
+//      into a second dense buffer (a feed-forward's inner activations beside the columns that
+//      ride along with its first projection)
 //   3  out bf16  [T, ldy] = silu(gate) * up     W rows are [64 gate | 64 up] per CTA (the host
 //                                                passes two tensor maps of the same matrix)
 //   4  QKV of heads of 128 dims, split K only: a CTA's 128 rows are one head; acc + bias is
@@ -145,6 +148,13 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, float (&v)[32]) {
 struct GemmArgs {
   const float* bias;  // [N] or null
   void* out;
+  // Mode 5: columns n >= act_from are not written to `out` but, after the xIELU activation
+  // (z > 0: a_pos z^2 + z / 2, else a_neg (exp(z) - 1 - z) + z / 2), to act_out [T, act_ld] at
+  // column n - act_from; columns below act_from go to `out` as in mode 0.
+  void* act_out;
+  long long act_ld;
+  int act_from;
+  float a_pos, a_neg;
   int* status;
   long long ldy;         // row pitch of out, in elements
   int T, N, K;
@@ -225,6 +235,21 @@ __device__ __forceinline__ void store_output(const GemmArgs& g, size_t index, fl
     // Nobody else adds to this element during the launch, so the sum is the same as with a load
     // and a store; as a reduction at the L2 it needs no round trip and threads do not wait for it.
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"((float*)g.out + index), "f"(value) : "memory");
+}
+
+// The same for a launch that knows token and column (all modes that reach store_output, and 5).
+__device__ __forceinline__ void store_output_at(const GemmArgs& g, int t, int n, float value) {
+  if (g.mode == 5) {
+    if (n < g.act_from) {
+      ((__nv_bfloat16*)g.out)[(size_t)t * g.ldy + n] = __float2bfloat16_rn(value);
+    } else {
+      const float z = value;
+      const float v = z > 0.f ? fmaf(g.a_pos * z, z, 0.5f * z) : fmaf(g.a_neg, (__expf(z) - 1.0f) - z, 0.5f * z);
+      ((__nv_bfloat16*)g.act_out)[(size_t)t * g.act_ld + (n - g.act_from)] = __float2bfloat16_rn(v);
+    }
+    return;
+  }
+  store_output(g, (size_t)t * g.ldy + n, value);
 }
 
 constexpr int GB_MAX_SPLITS = 8;  // CTAs of a cluster (a portable one; the device holds too few clusters of sixteen)
@@ -542,7 +567,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           if (n < g.N) {
             for (int j = 0; j < cols; ++j) {
               const int t = t0 + c0 + j;
-              if (t < g.T) store_output(g, (size_t)t * g.ldy + n, v[j] * (normed ? ssq_s[c0 + j] : 1.0f) + b);
+              if (t < g.T) store_output_at(g, t, n, v[j] * (normed ? ssq_s[c0 + j] : 1.0f) + b);
             }
           }
         }
@@ -671,7 +696,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         for (int peer = 0; peer < g.splits; ++peer)
           acc += recv[((size_t)peer * rows_per_cta + rl) * S::RECV_ROW + j];
         if (normed) acc *= ssq_s[j];
-        store_output(g, (size_t)t * g.ldy + n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
+        store_output_at(g, t, n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
       }
     }
     VX_TRACE_MARK(3);
@@ -1176,6 +1201,13 @@ static int floor_pow2(int value, int most) {
 // Returns 0 on launch, a cudaError_t on failure, -1 if the sizes are refused (K not a multiple
 // of 8, unaligned pointers, no driver entry point), or -2 if the fused norm's tiles do not fit
 // in shared memory (the caller then runs the norm by itself).
+struct ActArgs {
+  void* act_out;
+  long long act_ld;
+  int act_from;
+  float a_pos, a_neg;
+};
+
 struct RopeArgs {
   const int* positions;
   const float* cos_t;
@@ -1191,7 +1223,7 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
                      const float* norm_w, float eps, const void* w, const float* bias, void* out,
                      int mode, int T, int N, int K, long long ldy, int splits, int* status,
                      cudaStream_t stream, const RopeArgs* rope = nullptr, float* out2 = nullptr,
-                     long long ld2 = 0, int chunks = 1) {
+                     long long ld2 = 0, int chunks = 1, const ActArgs* act = nullptr) {
   if (T <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) != 0) return -1;
   const bool normed = resid != nullptr;
@@ -1200,7 +1232,7 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   if (normed && (T > 64 || norm_w == nullptr || (resid_ld % 4) != 0 ||
                  (reinterpret_cast<uintptr_t>(resid) & 15) || (reinterpret_cast<uintptr_t>(norm_w) & 15)))
     return -1;
-  if (mode < 0 || mode > 4 || (mode == 4) != (rope != nullptr)) return -1;
+  if (mode < 0 || mode > 5 || (mode == 4) != (rope != nullptr) || (mode == 5) != (act != nullptr)) return -1;
   const int bn = vx_gemm_bf16_token_tile(T);
   const int num_kb = (K + GB_BK - 1) / GB_BK;
   if (splits < 1 || mode == 3 || bn > 64) splits = 1;
@@ -1237,6 +1269,11 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   g.N = N;
   g.K = K;
   g.mode = mode;
+  g.act_out = act != nullptr ? act->act_out : nullptr;
+  g.act_ld = act != nullptr ? act->act_ld : 0;
+  g.act_from = act != nullptr ? act->act_from : 0;
+  g.a_pos = act != nullptr ? act->a_pos : 0.f;
+  g.a_neg = act != nullptr ? act->a_neg : 0.f;
   g.kb_per_split = (num_kb + splits - 1) / splits;
   g.splits = splits;
   // K in chunks of independent CTAs (mode 2 only): every CTA adds its partial tile to the output
@@ -1320,6 +1357,18 @@ VX_API int vx_gemm_bf16(const void* x, const void* w, const float* bias, void* o
                         int* status, cudaStream_t stream) {
   return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, bias, out, mode, T, N, K, ldy, splits,
                    status, stream);
+}
+
+// Mode 5: out[t, n] = acc + bias for columns n < act_from (bf16, pitch ldy); the other columns go
+// through the xIELU activation into act_out [T, act_ld] at column n - act_from.  One launch makes a
+// feed-forward's inner activations and the columns that ride along with its first projection.
+VX_API int vx_gemm_bf16_xielu(const void* x, const void* w, const float* bias, void* out, void* act_out, int T,
+                              int x_rows, int N, int K, long long ldy, long long act_ld, int act_from, float a_pos,
+                              float a_neg, int splits, int* status, cudaStream_t stream) {
+  if (act_out == nullptr || act_from < 0 || act_from > N) return -1;
+  const ActArgs act = {act_out, act_ld, act_from, a_pos, a_neg};
+  return gemm_bf16(x, x_rows, nullptr, 0, nullptr, 0.f, w, bias, out, 5, T, N, K, ldy, splits, status, stream, nullptr,
+                   nullptr, 0, 1, &act);
 }
 
 // Mode 2 (out += x w^T, float32) that also writes the sums to out2 [T, ld2]: a copy of the rows

@@ -15,7 +15,9 @@
 //                           rotation of every head's q_rot into the query row [q_abs | q_rot | 0]
 //   headwise_linear_kernel  out[t, h, :] = W[h] x[t, h, :] for every head, optionally times
 //                           sigmoid(gate[t, h]): the absorption of W_uk into the queries and
-//                           the expansion of the attention result by W_uv
+//                           the expansion of the attention result by W_uv (FP32 pipes; the
+//                           float32 path and inner sizes beyond the tensor-core form's)
+//   headwise_linear_mma_kernel  the same in bfloat16 on tensor-core tiles
 //
 // Rotation: dims 2i and 2i + 1 of the first 2 * rot_pairs dims are a pair (u, v) ->
 // (u cos a - v sin a, v cos a + u sin a), a = position * base^(-2i / (2 rot_pairs)); cos and sin
@@ -141,6 +143,145 @@ headwise_linear_kernel(const T* __restrict__ x, long long x_ld, int x_hs, const 
   }
 }
 
+// The same product on bf16 tensor-core tiles (mma.sync m16n8k16, float32 accumulators), for inner
+// sizes up to HT_MAX_K: a block takes a tile of tokens of one head (16 per warp) against a range
+// of outputs; inputs and the weight rows are staged in shared memory with the inner size
+// zero-padded to a multiple of 16.  The work is small (two products of [T, ~100] by
+// [~100, ~100] per head) and bound by its reads; what matters is that it does not run on the
+// FP32 pipes when T is in the thousands.  An output's sum does not depend on T or on the tile.
+constexpr int HT_MAX_K = 256;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Rows [0, rows) of a [*, K] matrix with row pitch `ld` into shared memory [*, pitch], columns
+// K .. kp zeroed; 16-byte copies when `vec` says that every row starts on a 16-byte boundary and K
+// is a multiple of 8.
+__device__ __forceinline__ void stage_rows(__nv_bfloat16* dst, int pitch, const __nv_bfloat16* src, long long ld,
+                                           int rows, int K, int kp, bool vec) {
+  const __nv_bfloat16 zero = __float2bfloat16_rn(0.f);
+  if (vec) {
+    // Four 16-byte loads under way per thread before the first store: the copy is bound by the
+    // latency of its loads, not by their number.
+    const int per_row = K / 8, total = rows * per_row;
+    for (int base = threadIdx.x; base < total; base += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * blockDim.x;
+        if (idx < total) {
+          const int r = idx / per_row, c = idx - r * per_row;
+          v[u] = *reinterpret_cast<const uint4*>(src + (size_t)r * ld + 8 * c);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * blockDim.x;
+        if (idx < total) {
+          const int r = idx / per_row, c = idx - r * per_row;
+          *reinterpret_cast<uint4*>(dst + r * pitch + 8 * c) = v[u];
+        }
+      }
+    }
+    for (int idx = threadIdx.x; idx < rows * (kp - K); idx += blockDim.x) {
+      const int r = idx / (kp - K), k = K + idx - r * (kp - K);
+      dst[r * pitch + k] = zero;
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < rows * kp; idx += blockDim.x) {
+      const int r = idx / kp, k = idx - r * kp;
+      dst[r * pitch + k] = k < K ? src[(size_t)r * ld + k] : zero;
+    }
+  }
+}
+
+// MW x 16 tokens of one head against NC outputs (blockIdx.z picks the range of outputs); warp
+// (m, n) of the MW x NW warps takes 16 tokens and NC / NW of the outputs.  Rows of the token tile
+// beyond the step's tokens are not staged: what the tensor cores make of them is never stored.
+template <int MW, int NW, int NC>
+__global__ void __launch_bounds__(MW * NW * 32)
+headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int x_hs,
+                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long out_ld,
+                           int out_hs, const __nv_bfloat16* __restrict__ gate, long long gate_ld, int num_tokens,
+                           int N, int K, int vec_x, int vec_w) {
+  extern __shared__ __align__(16) unsigned char ht_smem[];
+  constexpr int TOKENS = MW * 16, PER_WARP = NC / NW;
+  const int kp = (K + 15) / 16 * 16, pitch = kp + 8;  // +8 bf16: rows land in different banks
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ht_smem);  // [TOKENS][pitch]
+  __nv_bfloat16* ws = xs + TOKENS * pitch;                        // [NC][pitch]
+  const int t0 = blockIdx.x * TOKENS, h = blockIdx.y, n0 = blockIdx.z * NC;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, q = lane & 3;
+  const int n_here = min(NC, N - n0), t_here = min(TOKENS, num_tokens - t0);
+  allow_dependents();
+  // The weights do not depend on the kernel before this one.
+  stage_rows(ws, pitch, w + ((size_t)h * N + n0) * K, K, n_here, K, kp, vec_w != 0);
+  grid_dependency_wait();
+  stage_rows(xs, pitch, x + (size_t)t0 * x_ld + (size_t)h * x_hs, x_ld, t_here, K, kp, vec_x != 0);
+  const int r0 = (warp % MW) * 16 + g, r1 = r0 + 8;
+  const int c0 = (warp / MW) * PER_WARP;  // first output of this warp within the block's range
+  float gate0 = 1.f, gate1 = 1.f;
+  if (gate != nullptr) {
+    if (r0 < t_here) gate0 = 1.0f / (1.0f + expf(-to_float(gate[(size_t)(t0 + r0) * gate_ld + h])));
+    if (r1 < t_here) gate1 = 1.0f / (1.0f + expf(-to_float(gate[(size_t)(t0 + r1) * gate_ld + h])));
+  }
+  __syncthreads();
+  float acc[PER_WARP / 8][4];
+#pragma unroll
+  for (int j = 0; j < PER_WARP / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const int tiles = max(0, min(PER_WARP, n_here - c0) + 7) / 8;
+  for (int k0 = 0; k0 < kp; k0 += 16) {
+    uint32_t a[4];
+    a[0] = *reinterpret_cast<const uint32_t*>(xs + r0 * pitch + k0 + 2 * q);
+    a[1] = *reinterpret_cast<const uint32_t*>(xs + r1 * pitch + k0 + 2 * q);
+    a[2] = *reinterpret_cast<const uint32_t*>(xs + r0 * pitch + k0 + 8 + 2 * q);
+    a[3] = *reinterpret_cast<const uint32_t*>(xs + r1 * pitch + k0 + 8 + 2 * q);
+#pragma unroll
+    for (int j = 0; j < PER_WARP / 8; ++j) {
+      if (j < tiles) {
+        const __nv_bfloat16* wr = ws + (c0 + j * 8 + g) * pitch + k0 + 2 * q;
+        mma_bf16_16816(acc[j], a, *reinterpret_cast<const uint32_t*>(wr), *reinterpret_cast<const uint32_t*>(wr + 8));
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER_WARP / 8; ++j) {
+    if (j < tiles) {
+      const int n = c0 + j * 8 + 2 * q;
+      if (r0 < t_here) {
+        __nv_bfloat16* dst = out + (size_t)(t0 + r0) * out_ld + (size_t)h * out_hs + n0 + n;
+        if (n < n_here) dst[0] = __float2bfloat16_rn(acc[j][0] * gate0);
+        if (n + 1 < n_here) dst[1] = __float2bfloat16_rn(acc[j][1] * gate0);
+      }
+      if (r1 < t_here) {
+        __nv_bfloat16* dst = out + (size_t)(t0 + r1) * out_ld + (size_t)h * out_hs + n0 + n;
+        if (n < n_here) dst[0] = __float2bfloat16_rn(acc[j][2] * gate1);
+        if (n + 1 < n_here) dst[1] = __float2bfloat16_rn(acc[j][3] * gate1);
+      }
+    }
+  }
+}
+
+template <int MW, int NW, int NC>
+static int launch_headwise_mma(const void* x, long long x_ld, int x_hs, const void* w, void* out, long long out_ld,
+                               int out_hs, const void* gate, long long gate_ld, int num_tokens, int H, int N, int K,
+                               cudaStream_t stream) {
+  const int pitch = (K + 15) / 16 * 16 + 8;
+  const size_t bytes = sizeof(__nv_bfloat16) * (size_t)(MW * 16 + NC) * pitch;
+  if (bytes > 48 * 1024)
+    cudaFuncSetAttribute(headwise_linear_mma_kernel<MW, NW, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  const int vec_w = (K % 8) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  const int vec_x = (K % 8) == 0 && (x_ld % 8) == 0 && (x_hs % 8) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  launch_pdl(headwise_linear_mma_kernel<MW, NW, NC>, dim3((num_tokens + MW * 16 - 1) / (MW * 16), H, (N + NC - 1) / NC),
+             dim3(MW * NW * 32), bytes, stream, (const __nv_bfloat16*)x, x_ld, x_hs, (const __nv_bfloat16*)w,
+             (__nv_bfloat16*)out, out_ld, out_hs, (const __nv_bfloat16*)gate, gate_ld, num_tokens, N, K, vec_x, vec_w);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace vx
 
 using namespace vx;
@@ -170,6 +311,14 @@ VX_API int vx_headwise_linear(const void* x, long long x_ld, int x_hs, const voi
                               int N, int K, cudaStream_t stream) {
   if (num_tokens <= 0 || H <= 0 || N <= 0) return 0;
   if (K <= 0) return (int)cudaErrorInvalidValue;
+  if (dtype == VX_DTYPE_BF16 && K <= HT_MAX_K) {
+    // Few tokens: 16 tokens a block, its four warps 16 outputs each of a range of 64, so that the
+    // heads' weights are read by many blocks at once; many tokens: 64 tokens a block against 128
+    // outputs.
+    if (num_tokens <= 32)
+      return launch_headwise_mma<1, 4, 64>(x, x_ld, x_hs, w, out, out_ld, out_hs, gate, gate_ld, num_tokens, H, N, K, stream);
+    return launch_headwise_mma<4, 1, 128>(x, x_ld, x_hs, w, out, out_ld, out_hs, gate, gate_ld, num_tokens, H, N, K, stream);
+  }
   const size_t smem = sizeof(float) * HL_TOKENS * (size_t)K;
   if (smem > 96 * 1024) return -1;
   const dim3 grid((num_tokens + HL_TOKENS - 1) / HL_TOKENS, H);

@@ -189,6 +189,156 @@ __global__ void cast_rows_kernel(const float* __restrict__ in, __nv_bfloat16* __
     out[idx] = __float2bfloat16_rn(in[idx]);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Vector forms, for rows of whole chunks of four elements that start on the boundaries a chunk's
+// load needs (16 bytes in float32, 8 in bfloat16): a thread keeps up to GV_CHUNKS chunks in
+// registers across the two reductions.  The same formulas and the same order of sums per row.
+// ---------------------------------------------------------------------------------------------
+constexpr int GV_CHUNKS = 2;
+
+template <typename T>
+__device__ __forceinline__ float4 load4(const T* p);
+template <>
+__device__ __forceinline__ float4 load4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, float4 v);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, float4 v) {
+  *reinterpret_cast<float4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<const uint32_t*>(&a);
+  raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename T>
+__global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_out, const T* __restrict__ delta,
+                                          long long delta_ld, const T* __restrict__ gate, long long gate_ld,
+                                          const float* __restrict__ weight, float eps, int center,
+                                          T* __restrict__ lowp_out, const float* __restrict__ hist,
+                                          long long hist_stride, const float* __restrict__ mix_w, int mix_terms,
+                                          float* __restrict__ mix_out, int hidden) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
+  const int r = blockIdx.x;
+  const int chunks = hidden / 4;
+  const T* d = delta + (size_t)r * delta_ld;
+  const T* g = gate ? gate + (size_t)r * gate_ld : nullptr;
+  float4 y[GV_CHUNKS];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < GV_CHUNKS; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    y[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < chunks) {
+      y[j] = load4<T>(d + 4 * c);
+      if (g) {
+        const float4 e = load4<T>(g + 4 * c);
+        y[j].x *= sigmoid_f32(e.x);
+        y[j].y *= sigmoid_f32(e.y);
+        y[j].z *= sigmoid_f32(e.z);
+        y[j].w *= sigmoid_f32(e.w);
+      }
+    }
+    s += (y[j].x + y[j].y) + (y[j].z + y[j].w);
+  }
+  float mean = 0.f;
+  if (center) mean = block_sum(s, scratch) / (float)hidden;
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < GV_CHUNKS; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < chunks) {
+      const float a = y[j].x - mean, b = y[j].y - mean, e = y[j].z - mean, f = y[j].w - mean;
+      ss += (a * a + b * b) + (e * e + f * f);
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  const size_t row = (size_t)r * hidden;
+#pragma unroll
+  for (int j = 0; j < GV_CHUNKS; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c >= chunks) continue;
+    const float4 xin = *reinterpret_cast<const float4*>(resid_in + row + 4 * c);
+    const float4 wv = __ldg(reinterpret_cast<const float4*>(weight + 4 * c));
+    float4 x;
+    x.x = xin.x + (y[j].x - mean) * inv * wv.x;
+    x.y = xin.y + (y[j].y - mean) * inv * wv.y;
+    x.z = xin.z + (y[j].z - mean) * inv * wv.z;
+    x.w = xin.w + (y[j].w - mean) * inv * wv.w;
+    *reinterpret_cast<float4*>(resid_out + row + 4 * c) = x;
+    float4 going = x;
+    if (mix_terms > 0) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k + 1 < mix_terms; ++k) {
+        const float m = mix_w[k];
+        const float4 v = *reinterpret_cast<const float4*>(hist + (size_t)k * hist_stride + row + 4 * c);
+        acc.x = fmaf(m, v.x, acc.x);
+        acc.y = fmaf(m, v.y, acc.y);
+        acc.z = fmaf(m, v.z, acc.z);
+        acc.w = fmaf(m, v.w, acc.w);
+      }
+      const float m = mix_w[mix_terms - 1];
+      going = make_float4(fmaf(m, x.x, acc.x), fmaf(m, x.y, acc.y), fmaf(m, x.z, acc.z), fmaf(m, x.w, acc.w));
+      *reinterpret_cast<float4*>(mix_out + row + 4 * c) = going;
+    }
+    if (lowp_out) store4<T>(lowp_out + row + 4 * c, going);
+  }
+}
+
+// Eight (bfloat16) or four (float32) activations a thread; n, the row pitch and the pointers allow
+// 16-byte accesses.
+// The negative branch needs exp(z) - 1 - z.  float32 keeps expm1f (no cancellation near 0); in
+// bfloat16 the fast exponential's absolute error of about 1e-7 is far below what the result is
+// rounded to, and the accurate form would make the kernel compute-bound.
+template <typename T>
+__device__ __forceinline__ float exp_minus_one(float z);
+template <>
+__device__ __forceinline__ float exp_minus_one<float>(float z) { return expm1f(z); }
+template <>
+__device__ __forceinline__ float exp_minus_one<__nv_bfloat16>(float z) { return __expf(z) - 1.0f; }
+
+template <typename T>
+__global__ void xielu_vec_kernel(const T* __restrict__ in, long long in_ld, T* __restrict__ out, long long vectors,
+                                 int per_row, float a_pos, float a_neg) {
+  constexpr int W = 16 / (int)sizeof(T);
+  allow_dependents();
+  grid_dependency_wait();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < vectors; idx += stride) {
+    const long long t = idx / per_row;
+    const int c = (int)(idx - t * per_row);
+    const T* src = in + t * in_ld + (size_t)c * W;
+    T* dst = out + idx * W;
+#pragma unroll
+    for (int half = 0; half < W / 4; ++half) {
+      float4 z = load4<T>(src + 4 * half);
+      float* e = reinterpret_cast<float*>(&z);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        e[i] = e[i] > 0.f ? fmaf(a_pos * e[i], e[i], 0.5f * e[i]) : fmaf(a_neg, exp_minus_one<T>(e[i]) - e[i], 0.5f * e[i]);
+      store4<T>(dst + 4 * half, z);
+    }
+  }
+}
+
+static bool aligned_to(const void* p, int bytes) { return (reinterpret_cast<uintptr_t>(p) & (uintptr_t)(bytes - 1)) == 0; }
+
 static int row_threads(int hidden) {
   int threads = ((hidden + 3) / 4 + 31) / 32 * 32;
   return threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
@@ -226,6 +376,28 @@ VX_API int vx_gated_norm_add(const float* resid_in, float* resid_out, const void
   if (num_rows <= 0) return 0;
   if (mix_terms > 0 && (mix_w == nullptr || mix_out == nullptr || (mix_terms > 1 && hist == nullptr)))
     return (int)cudaErrorInvalidValue;
+  // Whole chunks of four that every pointer and pitch lets a thread load at once.
+  const int unit = dtype == VX_DTYPE_F32 ? 16 : 8, per = dtype == VX_DTYPE_F32 ? 4 : 2;
+  const bool vec = hidden % 4 == 0 && hidden / 4 <= 1024 * GV_CHUNKS && aligned_to(resid_in, 16) && aligned_to(resid_out, 16) &&
+                   aligned_to(weight, 16) && aligned_to(delta, unit) && (delta_ld * per) % unit == 0 &&
+                   (gate == nullptr || (aligned_to(gate, unit) && (gate_ld * per) % unit == 0)) &&
+                   (lowp_out == nullptr || aligned_to(lowp_out, unit)) &&
+                   (mix_terms == 0 || (aligned_to(mix_out, 16) && (hist == nullptr || (aligned_to(hist, 16) && hist_stride % 4 == 0))));
+  if (vec) {
+    const int chunks = hidden / 4;
+    int block = chunks <= 1024 ? chunks : (chunks + 1) / 2;
+    block = (block + 31) / 32 * 32;
+    if (block < 64) block = 64;
+    if (dtype == VX_DTYPE_F32)
+      launch_pdl(gated_norm_add_vec_kernel<float>, dim3(num_rows), dim3(block), 0, stream, resid_in, resid_out,
+                 (const float*)delta, delta_ld, (const float*)gate, gate_ld, weight, eps, center, (float*)lowp_out,
+                 hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
+    else
+      launch_pdl(gated_norm_add_vec_kernel<__nv_bfloat16>, dim3(num_rows), dim3(block), 0, stream, resid_in, resid_out,
+                 (const __nv_bfloat16*)delta, delta_ld, (const __nv_bfloat16*)gate, gate_ld, weight, eps, center,
+                 (__nv_bfloat16*)lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
+    return (int)cudaGetLastError();
+  }
   const int threads = row_threads(hidden);
   if (dtype == VX_DTYPE_F32)
     launch_pdl(gated_norm_add_kernel<float>, dim3(num_rows), dim3(threads), 0, stream, resid_in, resid_out,
@@ -242,6 +414,17 @@ VX_API int vx_xielu(const void* in, long long in_ld, void* out, int dtype, int n
                     float a_neg, cudaStream_t stream) {
   const long long total = (long long)num_rows * n;
   if (total <= 0) return 0;
+  const int width = dtype == VX_DTYPE_F32 ? 4 : 8;
+  if (n % width == 0 && in_ld % width == 0 && aligned_to(in, 16) && aligned_to(out, 16)) {
+    const long long vectors = total / width;
+    if (dtype == VX_DTYPE_F32)
+      launch_pdl(xielu_vec_kernel<float>, dim3(flat_blocks(vectors, 256)), dim3(256), 0, stream, (const float*)in, in_ld,
+                 (float*)out, vectors, n / width, a_pos, a_neg);
+    else
+      launch_pdl(xielu_vec_kernel<__nv_bfloat16>, dim3(flat_blocks(vectors, 256)), dim3(256), 0, stream,
+                 (const __nv_bfloat16*)in, in_ld, (__nv_bfloat16*)out, vectors, n / width, a_pos, a_neg);
+    return (int)cudaGetLastError();
+  }
   if (dtype == VX_DTYPE_F32)
     launch_pdl(xielu_kernel<float>, dim3(flat_blocks(total, 256)), dim3(256), 0, stream, (const float*)in, in_ld,
                (float*)out, total, n, a_pos, a_neg);

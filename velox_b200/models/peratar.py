@@ -11,9 +11,9 @@ output) instead of the last result alone.  The mixer caches a normalised latent 
 key part per token; a layer with ``kv_from`` reads the cache of that earlier layer.  After the
 last layer: layer norm, the head, and ``cap * tanh(logits / cap)``.
 
-The gates read the same rows as the sublayer they gate, so their matrices ride along as extra
-rows of that sublayer's first projection (``side_rows``): ``in.weight`` of the mixer is
-q | dkv | g | rg1 and ``up.weight`` of the feed-forward is up | rg2, concatenated in that order.
+The gates read the same rows as the sublayer they gate, so their matrices ride along as the
+first rows of that sublayer's first projection (``side_rows``): ``in.weight`` of the mixer is
+rg1 | q | dkv | g and ``up.weight`` of the feed-forward is rg2 | up, concatenated in that order.
 
 This module only maps configuration keys to part parameters and checkpoint names to part
 weights.  It has no forward pass.
@@ -64,11 +64,10 @@ def build_peratar_spec(config: ModelConfig) -> ModelSpec:
                 params={"rotary_dim": m.rot_dims, "base": m.rot_base, "max_position": c.max_position_embeddings},
             )
             positions[(m.rot_dims, m.rot_base)] = position
-        sources = [TensorSource(p + "mix.q", (H * (m.dim + m.rot_dim), E))]
+        sources = [TensorSource(p + "rg1", (E, E)), TensorSource(p + "mix.q", (H * (m.dim + m.rot_dim), E))]
         if own:
             sources.append(TensorSource(p + "mix.dkv", (m.kv_rank + m.rot_dim, E)))
         sources.append(TensorSource(p + "mix.g", (H, E)))
-        sources.append(TensorSource(p + "rg1", (E, E)))
         mixer_weights = {
             "in.weight": _matrix(*sources),
             "side.bias": _vector(TensorSource(p + "rg1.b", (E,))),
@@ -96,8 +95,8 @@ def build_peratar_spec(config: ModelConfig) -> ModelSpec:
                 kind="dense_xielu",
                 params={"hidden_size": E, "intermediate_size": F, "side_rows": E},
                 weights={
-                    "up.weight": _matrix(TensorSource(p + "mlp.up", (F, E)), TensorSource(p + "rg2", (E, E))),
-                    "up.bias": _vector(TensorSource(p + "mlp.up.b", (F,)), TensorSource(p + "rg2.b", (E,))),
+                    "up.weight": _matrix(TensorSource(p + "rg2", (E, E)), TensorSource(p + "mlp.up", (F, E))),
+                    "up.bias": _vector(TensorSource(p + "rg2.b", (E,)), TensorSource(p + "mlp.up.b", (F,))),
                     "down.weight": _matrix(TensorSource(p + "mlp.down", (E, F))),
                     "down.bias": _vector(TensorSource(p + "mlp.down.b", (E,))),
                     "act": _vector(TensorSource(p + "mlp.act", (2,))),

@@ -73,6 +73,10 @@ def core():
         lib.vx_gemm_bf16.argtypes = [
             _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
+        lib.vx_gemm_bf16_xielu.argtypes = [
+            _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_f, _c_f, _c_int,
+            _ptr, _ptr,
+        ]
         lib.vx_gemm_bf16_add_chunked.argtypes = [
             _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _ptr, _ptr,
         ]
@@ -614,6 +618,43 @@ def gemm_bf16(
             "multiple of 8 and both operands 16-byte aligned"
         )
     _check(code, "gemm_bf16")
+
+
+def gemm_bf16_xielu(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    out: torch.Tensor,
+    act_out: torch.Tensor,
+    act_from: int,
+    a_pos: float,
+    a_neg: float,
+    num_rows: int,
+    status: torch.Tensor,
+    splits: int = 1,
+) -> bool:
+    """``x[:num_rows] @ w.T + bias`` on the tensor-core kernel with the xIELU activation in its
+    epilogue: columns below ``act_from`` go to ``out`` as they are, the others, activated, to the
+    dense ``act_out`` [rows, N - act_from].  False (nothing launched) for sizes the kernel refuses."""
+    _need(x, torch.bfloat16, "x")
+    _need(w, torch.bfloat16, "w")
+    _need(out, torch.bfloat16, "out")
+    _need(act_out, torch.bfloat16, "act_out")
+    n, k = w.shape
+    if x.shape[1] != k or out.shape[1] < act_from or act_out.shape[1] != n - act_from:
+        raise ValueError(f"gemm_bf16_xielu shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, "
+                         f"out {tuple(out.shape)}, act_out {tuple(act_out.shape)}, act_from {act_from}")
+    if out.shape[0] < num_rows or act_out.shape[0] < num_rows:
+        raise ValueError("gemm_bf16_xielu: outputs do not hold the rows")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    code = core().vx_gemm_bf16_xielu(_p(x), _p(w), _p(bias), _p(out), _p(act_out), num_rows, x.shape[0], n, k,
+                                     out.stride(0), act_out.stride(0), int(act_from), float(a_pos), float(a_neg),
+                                     int(splits), _p(status), _stream())
+    if code == -1:
+        return False
+    _check(code, "gemm_bf16_xielu")
+    return True
 
 
 def gemm_bf16_add_chunked(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_rows: int,

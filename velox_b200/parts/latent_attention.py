@@ -6,7 +6,7 @@ share.  Head h's key is ``[W_uk[h] c | k_rot]`` and its value ``W_uv[h] c``; que
 head by head as ``[dim unrotated | rot_dim rotated]``.  Because the unrotated score
 ``q_u . (W_uk[h] c)`` equals ``(W_uk[h]^T q_u) . c``, the step never expands keys or values:
 
-    proj  = [W_q ; W_dkv ; W_g ; side rows] x            one projection of the layer's input
+    proj  = [side rows ; W_q ; W_dkv ; W_g] x            one projection of the layer's input
     c, k_rot -> cache;  q_rot rotated                    kernels.latent_prepare
     q_abs[h] = W_uk[h]^T q_u[h]                          kernels.headwise_linear
     o_lat[h] = softmax(([q_abs[h] | q_rot[h]] . [c | k_rot]) * scale) applied to the rows c
@@ -18,7 +18,7 @@ head by head as ``[dim unrotated | rot_dim rotated]``.  Because the unrotated sc
 A layer with ``own_latent`` false has no down projection: it reads the cache of the schedule entry
 named by the model's schedule (``cache.read_only``) with its own W_uk, W_uv and queries.
 
-``side_rows`` > 0: the last rows of ``in.weight`` are not the mixer's; their products (plus
+``side_rows`` > 0: the first rows of ``in.weight`` are not the mixer's; their products (plus
 ``side.bias``) belong to the block around it and are handed over as ``ctx.side_output``.
 """
 from __future__ import annotations
@@ -61,18 +61,22 @@ class LatentAttention(Mixer):
                 "largest row of 256"
             )
         H, q_head = self.num_heads, self.dim + self.rot_dim
-        self.q_width = H * q_head
-        self.latent_offset = self.q_width
-        self.gate_offset = self.q_width + (self.kv_rank + self.rot_dim if self.own_latent else 0)
-        self.side_offset = self.gate_offset + (H if self.gated else 0)
-        self.in_width = self.side_offset + self.side_rows
-        self.w_in = self.expect("in.weight", (self.in_width, self.hidden_size))
+        self.q_offset = self.side_rows
+        self.latent_offset = self.q_offset + H * q_head
+        self.gate_offset = self.latent_offset + (self.kv_rank + self.rot_dim if self.own_latent else 0)
+        rows = self.gate_offset + (H if self.gated else 0)
+        self.w_in = self.expect("in.weight", (rows, self.hidden_size))
+        # Rows of zeros up to a multiple of eight: the projection's output rows then start on
+        # 16-byte boundaries in bfloat16, which the library GEMM of long steps and the vector
+        # loads of the kernels that read the columns want.
+        self.in_width = -(-rows // 8) * 8
+        if self.in_width != rows:
+            self.w_in = torch.cat([self.w_in, self.w_in.new_zeros(self.in_width - rows, self.hidden_size)]).contiguous()
         self.b_in = None
         self.b_in_lowp = None
         if self.side_rows and "side.bias" in weights:
             side = self.expect("side.bias", (self.side_rows,))
-            self.b_in = torch.cat([torch.zeros(self.side_offset, dtype=torch.float32, device=side.device), side])
-            self.b_in = self.b_in.contiguous()
+            self.b_in = torch.cat([side, side.new_zeros(self.in_width - self.side_rows)]).contiguous()
             if dtype != torch.float32:
                 self.b_in_lowp = self.b_in.to(dtype)
         self.latent_norm = self.expect("latent_norm.weight", (self.kv_rank,)) if self.own_latent else None
@@ -99,16 +103,16 @@ class LatentAttention(Mixer):
         # reallocating one name (a captured step keeps the addresses it was captured with).
         proj = ws.get(f"latent.proj{self.in_width}", (ws.max_tokens, self.in_width), self.dtype)
         linear(x, self.w_in, self.b_in, proj, T, self.b_in_lowp, status=ctx.status)
-        ctx.side_output = proj[:, self.side_offset:] if self.side_rows else None
+        ctx.side_output = proj[:, : self.side_rows] if self.side_rows else None
 
         queries = ws.get(f"latent.queries{H * Dp}", (ws.max_tokens, H * Dp), self.dtype)
         group = ctx.groups[cache.group]
         kernels.latent_prepare(
-            proj, 0, self.latent_offset if self.own_latent else None, ctx.positions, self.position.cos,
+            proj, self.q_offset, self.latent_offset if self.own_latent else None, ctx.positions, self.position.cos,
             self.position.sin, self.latent_norm, self.eps, group.slot_mapping, cache.k,
             queries.view(ws.max_tokens, H, Dp), T, H, self.dim, self.rot_dim, self.kv_rank, ctx.status,
         )
-        kernels.headwise_linear(proj, 0, self.dim + self.rot_dim, self.w_uk_t, queries, 0, Dp, T)
+        kernels.headwise_linear(proj, self.q_offset, self.dim + self.rot_dim, self.w_uk_t, queries, 0, Dp, T)
 
         attn = ws.get(f"latent.attn{H * Dp}", (ws.max_tokens, H * Dp), self.dtype)
         plan = ctx.attention_plan(cache.group, self.attention_signature())

@@ -10,7 +10,7 @@ import os
 import torch
 
 from ..ops import kernels
-from ..ops.linear import DETERMINISTIC, linear, swiglu_linear, use_tensor_core_kernel
+from ..ops.linear import DETERMINISTIC, choose_splits, linear, swiglu_linear, use_tensor_core_kernel
 from .base import FeedForward
 from .registry import register_part
 
@@ -80,7 +80,7 @@ class DenseXielu(FeedForward):
     learned numbers p, q (``act`` weight): ``z > 0: softplus(p) z^2 + z / 2``, ``z <= 0:
     (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``, computed in float32.
 
-    ``side_rows`` > 0: the last rows of ``up.weight`` / ``up.bias`` are not the feed-forward's;
+    ``side_rows`` > 0: the first rows of ``up.weight`` / ``up.bias`` are not the feed-forward's;
     their products belong to the block around it (a gate over the result) and are handed over
     as ``ctx.side_output``, so the block's projection of the same input rides along."""
 
@@ -94,6 +94,11 @@ class DenseXielu(FeedForward):
         rows = self.intermediate_size + self.side_rows
         self.w_up = self.expect("up.weight", (rows, self.hidden_size))
         self.b_up = self.expect("up.bias", (rows,))
+        # Rows of zeros up to a multiple of eight (16-byte output rows in bfloat16).
+        self.up_width = -(-rows // 8) * 8
+        if self.up_width != rows:
+            self.w_up = torch.cat([self.w_up, self.w_up.new_zeros(self.up_width - rows, self.hidden_size)]).contiguous()
+            self.b_up = torch.cat([self.b_up, self.b_up.new_zeros(self.up_width - rows)]).contiguous()
         self.w_down = self.expect("down.weight", (self.hidden_size, self.intermediate_size))
         self.b_down = self.expect("down.bias", (self.hidden_size,))
         self.b_up_lowp = self.b_up.to(dtype) if dtype != torch.float32 else None
@@ -105,12 +110,19 @@ class DenseXielu(FeedForward):
     def forward(self, x, ctx):
         T = ctx.num_tokens
         ws = ctx.workspace
-        rows = self.intermediate_size + self.side_rows
+        rows = self.up_width
         up = ws.get(f"dense.up{rows}", (ws.max_tokens, rows), self.dtype)
-        linear(x, self.w_up, self.b_up, up, T, self.b_up_lowp, status=ctx.status)
-        ctx.side_output = up[:, self.intermediate_size:] if self.side_rows else None
+        ctx.side_output = up[:, : self.side_rows] if self.side_rows else None
         act = ws.get(f"dense.act{self.intermediate_size}", (ws.max_tokens, self.intermediate_size), self.dtype)
-        kernels.xielu(up, act, T, self.a_pos, self.a_neg)
+        # Few tokens: the activation is made in the projection's epilogue (the rows of zeros at
+        # the end of a padded matrix are left out of that launch).
+        fused = (ctx.status is not None and use_tensor_core_kernel(x, self.w_up, T)
+                 and kernels.gemm_bf16_xielu(x, self.w_up[: self.side_rows + self.intermediate_size],
+                                             self.b_up, up, act, self.side_rows, self.a_pos, self.a_neg, T,
+                                             ctx.status, splits=choose_splits(self.up_width, self.hidden_size, T)))
+        if not fused:
+            linear(x, self.w_up, self.b_up, up, T, self.b_up_lowp, status=ctx.status)
+            kernels.xielu(up[:, self.side_rows :], act, T, self.a_pos, self.a_neg)
         out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(act, self.w_down, self.b_down, out, T, self.b_down_lowp, status=ctx.status)
         return out
