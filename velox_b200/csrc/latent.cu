@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(MW * NW * 32)
 headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int x_hs,
                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long out_ld,
                            int out_hs, const __nv_bfloat16* __restrict__ gate, long long gate_ld, int num_tokens,
-                           int N, int K, int vec_x, int vec_w) {
+                           int N, int K, int vec_x, int vec_w, int pair_store) {
   extern __shared__ __align__(16) unsigned char ht_smem[];
   constexpr int TOKENS = MW * 16, PER_WARP = NC / NW;
   const int kp = (K + 15) / 16 * 16, pitch = kp + 8;  // +8 bf16: rows land in different banks
@@ -252,15 +252,24 @@ headwise_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, 
   for (int j = 0; j < PER_WARP / 8; ++j) {
     if (j < tiles) {
       const int n = c0 + j * 8 + 2 * q;
+      // Two neighbouring outputs as one 4-byte store where every row starts on an even element.
       if (r0 < t_here) {
         __nv_bfloat16* dst = out + (size_t)(t0 + r0) * out_ld + (size_t)h * out_hs + n0 + n;
-        if (n < n_here) dst[0] = __float2bfloat16_rn(acc[j][0] * gate0);
-        if (n + 1 < n_here) dst[1] = __float2bfloat16_rn(acc[j][1] * gate0);
+        if (pair_store && n + 1 < n_here) {
+          *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc[j][0] * gate0, acc[j][1] * gate0);
+        } else {
+          if (n < n_here) dst[0] = __float2bfloat16_rn(acc[j][0] * gate0);
+          if (n + 1 < n_here) dst[1] = __float2bfloat16_rn(acc[j][1] * gate0);
+        }
       }
       if (r1 < t_here) {
         __nv_bfloat16* dst = out + (size_t)(t0 + r1) * out_ld + (size_t)h * out_hs + n0 + n;
-        if (n < n_here) dst[0] = __float2bfloat16_rn(acc[j][2] * gate1);
-        if (n + 1 < n_here) dst[1] = __float2bfloat16_rn(acc[j][3] * gate1);
+        if (pair_store && n + 1 < n_here) {
+          *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc[j][2] * gate1, acc[j][3] * gate1);
+        } else {
+          if (n < n_here) dst[0] = __float2bfloat16_rn(acc[j][2] * gate1);
+          if (n + 1 < n_here) dst[1] = __float2bfloat16_rn(acc[j][3] * gate1);
+        }
       }
     }
   }
@@ -276,9 +285,10 @@ static int launch_headwise_mma(const void* x, long long x_ld, int x_hs, const vo
     cudaFuncSetAttribute(headwise_linear_mma_kernel<MW, NW, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   const int vec_w = (K % 8) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
   const int vec_x = (K % 8) == 0 && (x_ld % 8) == 0 && (x_hs % 8) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const int pair_store = (out_ld % 2) == 0 && (out_hs % 2) == 0 && (reinterpret_cast<uintptr_t>(out) & 3) == 0;
   launch_pdl(headwise_linear_mma_kernel<MW, NW, NC>, dim3((num_tokens + MW * 16 - 1) / (MW * 16), H, (N + NC - 1) / NC),
              dim3(MW * NW * 32), bytes, stream, (const __nv_bfloat16*)x, x_ld, x_hs, (const __nv_bfloat16*)w,
-             (__nv_bfloat16*)out, out_ld, out_hs, (const __nv_bfloat16*)gate, gate_ld, num_tokens, N, K, vec_x, vec_w);
+             (__nv_bfloat16*)out, out_ld, out_hs, (const __nv_bfloat16*)gate, gate_ld, num_tokens, N, K, vec_x, vec_w, pair_store);
   return (int)cudaGetLastError();
 }
 

@@ -192,9 +192,11 @@ __global__ void cast_rows_kernel(const float* __restrict__ in, __nv_bfloat16* __
 // ---------------------------------------------------------------------------------------------
 // Vector forms, for rows of whole chunks of four elements that start on the boundaries a chunk's
 // load needs (16 bytes in float32, 8 in bfloat16): a thread keeps up to GV_CHUNKS chunks in
-// registers across the two reductions.  The same formulas and the same order of sums per row.
+// registers across the two reductions: four warps a row and up to four chunks a thread (rows of
+// up to 2,048 elements), or eight warps and up to eight chunks (up to 8,192).  The same formulas;
+// the order of a row's sums depends on the row's length only.
 // ---------------------------------------------------------------------------------------------
-constexpr int GV_CHUNKS = 2;
+constexpr int GV_CHUNKS = 8;
 
 template <typename T>
 __device__ __forceinline__ float4 load4(const T* p);
@@ -224,7 +226,7 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
-template <typename T>
+template <typename T, int CHUNKS>
 __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_out, const T* __restrict__ delta,
                                           long long delta_ld, const T* __restrict__ gate, long long gate_ld,
                                           const float* __restrict__ weight, float eps, int center,
@@ -238,21 +240,29 @@ __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_ou
   const int chunks = hidden / 4;
   const T* d = delta + (size_t)r * delta_ld;
   const T* g = gate ? gate + (size_t)r * gate_ld : nullptr;
-  float4 y[GV_CHUNKS];
-  float s = 0.f;
+  const size_t row = (size_t)r * hidden;
+  // Everything the row needs is asked for before the first reduction: the sublayer's result and
+  // its gate, and the stream's rows and the weight that are only used after the second one.
+  float4 y[CHUNKS], e[CHUNKS], xin[CHUNKS], wv[CHUNKS];
 #pragma unroll
-  for (int j = 0; j < GV_CHUNKS; ++j) {
+  for (int j = 0; j < CHUNKS; ++j) {
     const int c = threadIdx.x + j * blockDim.x;
-    y[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    y[j] = e[j] = xin[j] = wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < chunks) {
       y[j] = load4<T>(d + 4 * c);
-      if (g) {
-        const float4 e = load4<T>(g + 4 * c);
-        y[j].x *= sigmoid_f32(e.x);
-        y[j].y *= sigmoid_f32(e.y);
-        y[j].z *= sigmoid_f32(e.z);
-        y[j].w *= sigmoid_f32(e.w);
-      }
+      if (g) e[j] = load4<T>(g + 4 * c);
+      xin[j] = *reinterpret_cast<const float4*>(resid_in + row + 4 * c);
+      wv[j] = __ldg(reinterpret_cast<const float4*>(weight + 4 * c));
+    }
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    if (g) {
+      y[j].x *= sigmoid_f32(e[j].x);
+      y[j].y *= sigmoid_f32(e[j].y);
+      y[j].z *= sigmoid_f32(e[j].z);
+      y[j].w *= sigmoid_f32(e[j].w);
     }
     s += (y[j].x + y[j].y) + (y[j].z + y[j].w);
   }
@@ -260,27 +270,24 @@ __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_ou
   if (center) mean = block_sum(s, scratch) / (float)hidden;
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < GV_CHUNKS; ++j) {
+  for (int j = 0; j < CHUNKS; ++j) {
     const int c = threadIdx.x + j * blockDim.x;
     if (c < chunks) {
-      const float a = y[j].x - mean, b = y[j].y - mean, e = y[j].z - mean, f = y[j].w - mean;
-      ss += (a * a + b * b) + (e * e + f * f);
+      const float a = y[j].x - mean, b = y[j].y - mean, p = y[j].z - mean, q = y[j].w - mean;
+      ss += (a * a + b * b) + (p * p + q * q);
     }
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
-  const size_t row = (size_t)r * hidden;
 #pragma unroll
-  for (int j = 0; j < GV_CHUNKS; ++j) {
+  for (int j = 0; j < CHUNKS; ++j) {
     const int c = threadIdx.x + j * blockDim.x;
     if (c >= chunks) continue;
-    const float4 xin = *reinterpret_cast<const float4*>(resid_in + row + 4 * c);
-    const float4 wv = __ldg(reinterpret_cast<const float4*>(weight + 4 * c));
     float4 x;
-    x.x = xin.x + (y[j].x - mean) * inv * wv.x;
-    x.y = xin.y + (y[j].y - mean) * inv * wv.y;
-    x.z = xin.z + (y[j].z - mean) * inv * wv.z;
-    x.w = xin.w + (y[j].w - mean) * inv * wv.w;
+    x.x = xin[j].x + (y[j].x - mean) * inv * wv[j].x;
+    x.y = xin[j].y + (y[j].y - mean) * inv * wv[j].y;
+    x.z = xin[j].z + (y[j].z - mean) * inv * wv[j].z;
+    x.w = xin[j].w + (y[j].w - mean) * inv * wv[j].w;
     *reinterpret_cast<float4*>(resid_out + row + 4 * c) = x;
     float4 going = x;
     if (mix_terms > 0) {
@@ -299,6 +306,17 @@ __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_ou
     }
     if (lowp_out) store4<T>(lowp_out + row + 4 * c, going);
   }
+}
+
+template <typename T, int CHUNKS>
+static void launch_gated_norm_add_vec(int block, const float* resid_in, float* resid_out, const void* delta,
+                                      long long delta_ld, const void* gate, long long gate_ld, const float* weight,
+                                      float eps, int center, void* lowp_out, const float* hist, long long hist_stride,
+                                      const float* mix_w, int mix_terms, float* mix_out, int num_rows, int hidden,
+                                      cudaStream_t stream) {
+  launch_pdl(gated_norm_add_vec_kernel<T, CHUNKS>, dim3(num_rows), dim3(block), 0, stream, resid_in, resid_out,
+             (const T*)delta, delta_ld, (const T*)gate, gate_ld, weight, eps, center, (T*)lowp_out, hist, hist_stride,
+             mix_w, mix_terms, mix_out, hidden);
 }
 
 // Eight (bfloat16) or four (float32) activations a thread; n, the row pitch and the pointers allow
@@ -378,24 +396,25 @@ VX_API int vx_gated_norm_add(const float* resid_in, float* resid_out, const void
     return (int)cudaErrorInvalidValue;
   // Whole chunks of four that every pointer and pitch lets a thread load at once.
   const int unit = dtype == VX_DTYPE_F32 ? 16 : 8, per = dtype == VX_DTYPE_F32 ? 4 : 2;
-  const bool vec = hidden % 4 == 0 && hidden / 4 <= 1024 * GV_CHUNKS && aligned_to(resid_in, 16) && aligned_to(resid_out, 16) &&
+  const bool vec = hidden % 4 == 0 && hidden / 4 <= 256 * GV_CHUNKS && aligned_to(resid_in, 16) && aligned_to(resid_out, 16) &&
                    aligned_to(weight, 16) && aligned_to(delta, unit) && (delta_ld * per) % unit == 0 &&
                    (gate == nullptr || (aligned_to(gate, unit) && (gate_ld * per) % unit == 0)) &&
                    (lowp_out == nullptr || aligned_to(lowp_out, unit)) &&
                    (mix_terms == 0 || (aligned_to(mix_out, 16) && (hist == nullptr || (aligned_to(hist, 16) && hist_stride % 4 == 0))));
   if (vec) {
     const int chunks = hidden / 4;
-    int block = chunks <= 1024 ? chunks : (chunks + 1) / 2;
-    block = (block + 31) / 32 * 32;
-    if (block < 64) block = 64;
-    if (dtype == VX_DTYPE_F32)
-      launch_pdl(gated_norm_add_vec_kernel<float>, dim3(num_rows), dim3(block), 0, stream, resid_in, resid_out,
-                 (const float*)delta, delta_ld, (const float*)gate, gate_ld, weight, eps, center, (float*)lowp_out,
-                 hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
-    else
-      launch_pdl(gated_norm_add_vec_kernel<__nv_bfloat16>, dim3(num_rows), dim3(block), 0, stream, resid_in, resid_out,
-                 (const __nv_bfloat16*)delta, delta_ld, (const __nv_bfloat16*)gate, gate_ld, weight, eps, center,
-                 (__nv_bfloat16*)lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
+    const int block = chunks <= 128 * 4 ? 128 : 256;
+    const int per = (chunks + block - 1) / block;
+#define VX_GNA(T, C)                                                                                              \
+  launch_gated_norm_add_vec<T, C>(block, resid_in, resid_out, delta, delta_ld, gate, gate_ld, weight, eps, center, \
+                                  lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, num_rows, hidden, stream)
+    if (dtype == VX_DTYPE_F32) {
+      if (per <= 1) VX_GNA(float, 1); else if (per <= 2) VX_GNA(float, 2); else if (per <= 4) VX_GNA(float, 4); else VX_GNA(float, 8);
+    } else {
+      if (per <= 1) VX_GNA(__nv_bfloat16, 1); else if (per <= 2) VX_GNA(__nv_bfloat16, 2);
+      else if (per <= 4) VX_GNA(__nv_bfloat16, 4); else VX_GNA(__nv_bfloat16, 8);
+    }
+#undef VX_GNA
     return (int)cudaGetLastError();
   }
   const int threads = row_threads(hidden);
