@@ -64,13 +64,18 @@ def test_registry_picks_the_model_by_architecture(tmp_path):
 
 
 def test_named_model_sizes_are_configurations_of_the_architecture():
-    """Every --model-size name parses as this architecture; 1.5b has the sizes the benchmark names."""
+    """Every --model-size name parses as its architecture; 1.5b has the sizes the benchmark names."""
     from velox_b200.config import Qwen2Config, architecture_of
     from velox_b200.config.presets import MODEL_SIZES, model_size
 
     for name in MODEL_SIZES:
         cfg = model_size(name)
-        assert architecture_of(cfg).name == "Qwen2ForCausalLM"
+        arch = architecture_of(cfg)
+        typed = arch.parse_config(cfg)
+        if name.startswith("peratar-"):
+            assert arch.name == "Peratar" and typed.num_hidden_layers == len(cfg["layers"])
+            continue
+        assert arch.name == "Qwen2ForCausalLM"
         c = Qwen2Config.from_dict(cfg)
         assert c.num_attention_heads % c.num_key_value_heads == 0
     c = Qwen2Config.from_dict(model_size("1.5b"))

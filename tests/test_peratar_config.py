@@ -157,3 +157,23 @@ def test_plain_model_is_causal_and_uses_the_shared_cache():
     changed = dict(tensors)
     changed["l0.mix.dkv"] = tensors["l0.mix.dkv"] * 1.5
     assert not torch.allclose(plain.forward_logits(changed, pc.SMALL, tokens), full, atol=1e-3)
+
+
+def test_presets_at_the_qwen_widths_and_other_layer_counts():
+    from velox_b200.config.presets import model_size, with_layers
+
+    cfg = model_size("peratar-1.5b")
+    twin = model_size("1.5b")
+    assert cfg["width"] == twin["hidden_size"] and len(cfg["layers"]) == twin["num_hidden_layers"]
+    for count in (1, 2, 5, 40):
+        typed = PeratarConfig.from_dict(with_layers(cfg, count))
+        assert typed.num_hidden_layers == count
+        for index, layer in enumerate(typed.layers):
+            assert layer.mixer.kv_from in (None, index - 1)
+    assert with_layers(twin, 3)["num_hidden_layers"] == 3
+    # a layer's weights are about as many bytes as its twin's
+    from velox_b200.cli.roofline import layer_bytes
+
+    mine, _ = layer_bytes(cfg, 1, 1)
+    theirs, _ = layer_bytes(twin, 1, 1)
+    assert 0.9 < mine / theirs < 1.1

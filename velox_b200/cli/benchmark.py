@@ -244,7 +244,9 @@ def main(argv: Optional[List[str]] = None) -> int:
             with open(args.random_weights, "r", encoding="utf-8") as handle:
                 config_json = json.load(handle)
         if args.layers is not None:
-            config_json["num_hidden_layers"] = args.layers
+            from ..config.presets import with_layers
+
+            config_json = with_layers(config_json, args.layers)
         holder = tempfile.TemporaryDirectory(prefix="velox_model_")
         model_dir = holder.name
         write_random_model(model_dir, config_json, seed=args.weights_seed, dtype="bfloat16")

@@ -81,13 +81,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     import torch
 
     from ..config import EngineConfig
-    from ..config.presets import model_size
+    from ..config.presets import model_size, with_layers
     from ..engine.engine import Engine
     from ..engine.runner import StepChunk
     from ..ops import kernels
     from ..weights import write_random_model
 
-    config_json = dict(model_size(args.model_size), num_hidden_layers=args.layers)
+    config_json = with_layers(model_size(args.model_size), args.layers)
     tokens = max(args.prefill, 1)
     seqs = 1 if args.prefill else args.batch
     most_keys = args.context + tokens + 16
@@ -98,7 +98,11 @@ def main(argv: Optional[List[str]] = None) -> int:
             max_num_batched_tokens=max(256, tokens, seqs), max_prefill_chunk_size=max(256, tokens),
             block_size=args.block_size, num_gpu_blocks=seqs * (-(-most_keys // args.block_size) + 1) + 8, seed=0))
     runner, cache = engine.runner, engine.cache
-    head_dim = config_json.get("head_dim") or config_json["hidden_size"] // config_json["num_attention_heads"]
+    if "layers" in config_json:  # a design that lists its layers: the width of its cached rows
+        mixer = config_json["layers"][0]["mixer"]
+        head_dim = -(-(mixer["kv_rank"] + mixer["rot_dim"]) // 16) * 16
+    else:
+        head_dim = config_json.get("head_dim") or config_json["hidden_size"] // config_json["num_attention_heads"]
 
     def one_step():
         held = []

@@ -21,6 +21,12 @@ namespace vx {
 constexpr int RN_MAX_PER_THREAD = 8;
 
 __device__ __forceinline__ float sigmoid_f32(float v) { return 1.0f / (1.0f + expf(-v)); }
+// The gate of a row whose sublayer result and gate logits are bfloat16: the fast exponential and
+// division are exact far beyond what the operands carry.  float32 rows keep the accurate form.
+template <typename T>
+__device__ __forceinline__ float gate_sigmoid(float v) { return sigmoid_f32(v); }
+template <>
+__device__ __forceinline__ float gate_sigmoid<__nv_bfloat16>(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
 
 // Mean (0 when `center` is off) and 1 / sqrt(mean((v - mean)^2) + eps) of a row given by
 // `value(i)`; two passes over the row, as the definition says.  `vals` caches the row when it
@@ -259,10 +265,10 @@ __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_ou
 #pragma unroll
   for (int j = 0; j < CHUNKS; ++j) {
     if (g) {
-      y[j].x *= sigmoid_f32(e[j].x);
-      y[j].y *= sigmoid_f32(e[j].y);
-      y[j].z *= sigmoid_f32(e[j].z);
-      y[j].w *= sigmoid_f32(e[j].w);
+      y[j].x *= gate_sigmoid<T>(e[j].x);
+      y[j].y *= gate_sigmoid<T>(e[j].y);
+      y[j].z *= gate_sigmoid<T>(e[j].z);
+      y[j].w *= gate_sigmoid<T>(e[j].w);
     }
     s += (y[j].x + y[j].y) + (y[j].z + y[j].w);
   }
@@ -279,32 +285,53 @@ __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_ou
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  float4 x[CHUNKS];
 #pragma unroll
   for (int j = 0; j < CHUNKS; ++j) {
+    x[j].x = xin[j].x + (y[j].x - mean) * inv * wv[j].x;
+    x[j].y = xin[j].y + (y[j].y - mean) * inv * wv[j].y;
+    x[j].z = xin[j].z + (y[j].z - mean) * inv * wv[j].z;
+    x[j].w = xin[j].w + (y[j].w - mean) * inv * wv[j].w;
     const int c = threadIdx.x + j * blockDim.x;
-    if (c >= chunks) continue;
-    float4 x;
-    x.x = xin[j].x + (y[j].x - mean) * inv * wv[j].x;
-    x.y = xin[j].y + (y[j].y - mean) * inv * wv[j].y;
-    x.z = xin[j].z + (y[j].z - mean) * inv * wv[j].z;
-    x.w = xin[j].w + (y[j].w - mean) * inv * wv[j].w;
-    *reinterpret_cast<float4*>(resid_out + row + 4 * c) = x;
-    float4 going = x;
-    if (mix_terms > 0) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int k = 0; k + 1 < mix_terms; ++k) {
-        const float m = mix_w[k];
-        const float4 v = *reinterpret_cast<const float4*>(hist + (size_t)k * hist_stride + row + 4 * c);
-        acc.x = fmaf(m, v.x, acc.x);
-        acc.y = fmaf(m, v.y, acc.y);
-        acc.z = fmaf(m, v.z, acc.z);
-        acc.w = fmaf(m, v.w, acc.w);
+    if (c < chunks) *reinterpret_cast<float4*>(resid_out + row + 4 * c) = x[j];
+  }
+  if (mix_terms > 0) {
+    // One earlier result at a time, all of the thread's chunks of it asked for at once.
+    float4 acc[CHUNKS];
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k + 1 < mix_terms; ++k) {
+      const float m = mix_w[k];
+      const float* src = hist + (size_t)k * hist_stride + row;
+      float4 v[CHUNKS];
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        v[j] = c < chunks ? *reinterpret_cast<const float4*>(src + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      const float m = mix_w[mix_terms - 1];
-      going = make_float4(fmaf(m, x.x, acc.x), fmaf(m, x.y, acc.y), fmaf(m, x.z, acc.z), fmaf(m, x.w, acc.w));
-      *reinterpret_cast<float4*>(mix_out + row + 4 * c) = going;
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        acc[j].x = fmaf(m, v[j].x, acc[j].x);
+        acc[j].y = fmaf(m, v[j].y, acc[j].y);
+        acc[j].z = fmaf(m, v[j].z, acc[j].z);
+        acc[j].w = fmaf(m, v[j].w, acc[j].w);
+      }
     }
-    if (lowp_out) store4<T>(lowp_out + row + 4 * c, going);
+    const float m = mix_w[mix_terms - 1];
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      x[j] = make_float4(fmaf(m, x[j].x, acc[j].x), fmaf(m, x[j].y, acc[j].y), fmaf(m, x[j].z, acc[j].z),
+                         fmaf(m, x[j].w, acc[j].w));
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < chunks) *reinterpret_cast<float4*>(mix_out + row + 4 * c) = x[j];
+    }
+  }
+  if (lowp_out) {
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < chunks) store4<T>(lowp_out + row + 4 * c, x[j]);
+    }
   }
 }
 
