@@ -72,7 +72,7 @@ def test_named_model_sizes_are_configurations_of_the_architecture():
         cfg = model_size(name)
         arch = architecture_of(cfg)
         typed = arch.parse_config(cfg)
-        if name.startswith("peratar-"):
+        if name.startswith("peratar-") or name == "tiny-p":
             assert arch.name == "Peratar" and typed.num_hidden_layers == len(cfg["layers"])
             continue
         assert arch.name == "Qwen2ForCausalLM"

@@ -93,6 +93,14 @@ def test_gated_join_and_depth_mix(dtype, width, terms):
     # without a gate
     kernels.gated_norm_add(x_in, x_out, delta, None, weight, 1e-5, False, rows)
     close(x_out, x_in.double() + plain.rms_norm(delta.double(), weight.double(), 1e-5), dtype, "ungated rms join")
+    # the result as float32 sums with a bias still to add; the rows read are handed back empty
+    sums = torch.randn(rows + 2, width, generator=gen).cuda()
+    bias = torch.randn(width, generator=gen).cuda()
+    kept = sums.clone()
+    kernels.gated_norm_add(x_in, x_out, None, gate, weight, 1e-5, True, rows, sums=sums, sums_bias=bias, compute_dtype=dt)
+    y = (kept[:rows].double() + bias.double()) * torch.sigmoid(gate.double())
+    close(x_out, x_in.double() + plain.layer_norm(y, weight.double(), 1e-5), dtype, "join of float32 sums")
+    assert torch.all(sums[:rows] == 0) and torch.equal(sums[rows:], kept[rows:])
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
@@ -439,6 +447,26 @@ def test_layer_streams(models, dtype):
             # single elements behind such a norm can be off by several per cent; the rows are not
             relative = float((got - want).norm() / want.norm())
             assert relative <= 3e-2, f"slot {index} of the store of results: relative error {relative:.3f}"
+
+
+def test_command_lines_take_the_design(tmp_path, capsys):
+    """The benchmark and roofline command lines on the tiny named size of the design."""
+    import json
+
+    from velox_b200.cli import benchmark, roofline
+
+    common = ["--model-size", "tiny-p", "--num-requests", "5", "--max-tokens", "10", "--max-model-len", "128",
+              "--max-num-seqs", "4", "--max-num-batched-tokens", "64", "--max-prefill-chunk-size", "16",
+              "--block-size", "8", "--workload", "short", "--seed", "3"]
+    assert benchmark.main(common + ["--temperature", "0"]) == 0
+    assert "decode throughput" in capsys.readouterr().out
+    assert benchmark.main(common + ["--temperature", "0.7", "--top-k", "10", "--layers", "2", "--no-pipeline"]) == 0
+    capsys.readouterr()
+    table = tmp_path / "roofline.json"
+    assert roofline.main(["--model-size", "tiny-p", "--batch", "2", "--context", "40", "--layers", "1,3", "--steps", "4",
+                          "--warmup", "1", "--block-size", "8", "--output-json", str(table)]) == 0
+    rows = json.loads(table.read_text())
+    assert rows[0]["us_by_bytes"] > 0 and rows[0]["size"] == "tiny-p"
 
 
 def test_greedy_generation_through_the_engine(models):

@@ -58,7 +58,27 @@ def _peratar(like: str, rot_dim: int = 32, kv_rank: int = 96, share_every: int =
             "logit_softcap": 30.0, "layers": entries, "max_position_embeddings": base["max_position_embeddings"]}
 
 
+def _peratar_tiny() -> Dict[str, Any]:
+    """A tiny Peratar configuration for smoke runs of the command lines: three layers of different
+    sizes, the second without feed-forward, the third on the first one's cache."""
+    def mixer(heads, dim, rot_dim, vdim, kv_rank, scale, kv_from=None):
+        out = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "scale": scale,
+               "rot": {"base": 10000.0, "dims": rot_dim}}
+        if kv_from is not None:
+            out["kv_from"] = kv_from
+        return out
+
+    layers = [
+        {"type": "latent_attention", "mixer": mixer(4, 16, 8, 16, 24, 0.2), "mlp": {"kind": "dense", "ff": 160}},
+        {"type": "latent_attention", "mixer": mixer(2, 24, 16, 32, 32, 0.15), "mlp": None},
+        {"type": "latent_attention", "mixer": mixer(4, 8, 8, 24, 24, 0.25, kv_from=0), "mlp": {"kind": "dense", "ff": 96}},
+    ]
+    return {"architecture": "Peratar", "vocab": 384, "width": 128, "norm": {"eps": 1e-5}, "logit_softcap": 20.0,
+            "layers": layers, "max_position_embeddings": 512}
+
+
 MODEL_SIZES.update({
+    "tiny-p": _peratar_tiny(),
     "peratar-0.5b": _peratar("0.5b"),
     "peratar-1.5b": _peratar("1.5b"),
     "peratar-3b": _peratar("3b"),

@@ -106,6 +106,9 @@ __global__ void norm_rows_kernel(float* __restrict__ resid, const T* __restrict_
 // ---------------------------------------------------------------------------------------------
 // A sublayer's result joins the stream:
 //   y        = delta[r] * sigmoid(gate[r])            (gate null: y = delta[r])
+//              delta32 given instead of delta: the result lies in a float32 buffer into which a
+//              projection has added its shares (y uses delta32[r] + delta_bias), and the rows
+//              read are set to zero again, so that the next sums start from nothing
 //   x        = resid_in[r] + norm(y) * weight         -> resid_out[r]
 //   outgoing = x                                      (mix_terms == 0)
 //            = sum_{j < mix_terms - 1} mix_w[j] * hist[j][r]  +  mix_w[mix_terms - 1] * x
@@ -120,15 +123,18 @@ __global__ void gated_norm_add_kernel(const float* resid_in, float* resid_out, c
                                       const float* __restrict__ weight, float eps, int center,
                                       T* __restrict__ lowp_out, const float* __restrict__ hist,
                                       long long hist_stride, const float* __restrict__ mix_w, int mix_terms,
-                                      float* __restrict__ mix_out, int hidden) {
+                                      float* __restrict__ mix_out, int hidden, float* __restrict__ delta32,
+                                      long long delta32_ld, const float* __restrict__ delta_bias) {
   __shared__ float scratch[32];
   allow_dependents();
   grid_dependency_wait();
   const int r = blockIdx.x;
-  const T* d = delta + (size_t)r * delta_ld;
+  const T* d = delta ? delta + (size_t)r * delta_ld : nullptr;
+  float* d32 = delta32 ? delta32 + (size_t)r * delta32_ld : nullptr;
   const T* g = gate ? gate + (size_t)r * gate_ld : nullptr;
   auto value = [&](int i) {
-    const float v = to_float(d[i]);
+    float v = d32 ? d32[i] : to_float(d[i]);
+    if (delta_bias) v += delta_bias[i];
     return g ? v * sigmoid_f32(to_float(g[i])) : v;
   };
   const bool cached = hidden <= RN_MAX_PER_THREAD * (int)blockDim.x;
@@ -148,6 +154,7 @@ __global__ void gated_norm_add_kernel(const float* resid_in, float* resid_out, c
       mix_out[(size_t)r * hidden + i] = outgoing;
     }
     if (lowp_out) lowp_out[(size_t)r * hidden + i] = from_float<T>(outgoing);
+    if (d32) d32[i] = 0.f;  // the sums' buffer is handed back empty
   };
   if (cached) {
 #pragma unroll
@@ -238,13 +245,15 @@ __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_ou
                                           const float* __restrict__ weight, float eps, int center,
                                           T* __restrict__ lowp_out, const float* __restrict__ hist,
                                           long long hist_stride, const float* __restrict__ mix_w, int mix_terms,
-                                          float* __restrict__ mix_out, int hidden) {
+                                          float* __restrict__ mix_out, int hidden, float* __restrict__ delta32,
+                                          long long delta32_ld, const float* __restrict__ delta_bias) {
   __shared__ float scratch[32];
   allow_dependents();
   grid_dependency_wait();
   const int r = blockIdx.x;
   const int chunks = hidden / 4;
-  const T* d = delta + (size_t)r * delta_ld;
+  const T* d = delta ? delta + (size_t)r * delta_ld : nullptr;
+  float* d32 = delta32 ? delta32 + (size_t)r * delta32_ld : nullptr;
   const T* g = gate ? gate + (size_t)r * gate_ld : nullptr;
   const size_t row = (size_t)r * hidden;
   // Everything the row needs is asked for before the first reduction: the sublayer's result and
@@ -255,10 +264,24 @@ __global__ void gated_norm_add_vec_kernel(const float* resid_in, float* resid_ou
     const int c = threadIdx.x + j * blockDim.x;
     y[j] = e[j] = xin[j] = wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c < chunks) {
-      y[j] = load4<T>(d + 4 * c);
+      y[j] = d32 ? *reinterpret_cast<const float4*>(d32 + 4 * c) : load4<T>(d + 4 * c);
+      if (delta_bias) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(delta_bias + 4 * c));
+        y[j].x += b.x;
+        y[j].y += b.y;
+        y[j].z += b.z;
+        y[j].w += b.w;
+      }
       if (g) e[j] = load4<T>(g + 4 * c);
       xin[j] = *reinterpret_cast<const float4*>(resid_in + row + 4 * c);
       wv[j] = __ldg(reinterpret_cast<const float4*>(weight + 4 * c));
+    }
+  }
+  if (d32) {  // the sums' buffer is handed back empty
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < chunks) *reinterpret_cast<float4*>(d32 + 4 * c) = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }
   float s = 0.f;
@@ -340,10 +363,11 @@ static void launch_gated_norm_add_vec(int block, const float* resid_in, float* r
                                       long long delta_ld, const void* gate, long long gate_ld, const float* weight,
                                       float eps, int center, void* lowp_out, const float* hist, long long hist_stride,
                                       const float* mix_w, int mix_terms, float* mix_out, int num_rows, int hidden,
+                                      float* delta32, long long delta32_ld, const float* delta_bias,
                                       cudaStream_t stream) {
   launch_pdl(gated_norm_add_vec_kernel<T, CHUNKS>, dim3(num_rows), dim3(block), 0, stream, resid_in, resid_out,
              (const T*)delta, delta_ld, (const T*)gate, gate_ld, weight, eps, center, (T*)lowp_out, hist, hist_stride,
-             mix_w, mix_terms, mix_out, hidden);
+             mix_w, mix_terms, mix_out, hidden, delta32, delta32_ld, delta_bias);
 }
 
 // Eight (bfloat16) or four (float32) activations a thread; n, the row pitch and the pointers allow
@@ -417,14 +441,18 @@ VX_API int vx_gated_norm_add(const float* resid_in, float* resid_out, const void
                              const void* gate, long long gate_ld, const float* weight, float eps, int center,
                              void* lowp_out, int dtype, const float* hist, long long hist_stride,
                              const float* mix_w, int mix_terms, float* mix_out, int num_rows, int hidden,
-                             cudaStream_t stream) {
+                             float* delta32, long long delta32_ld, const float* delta_bias, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
+  if ((delta == nullptr) == (delta32 == nullptr)) return (int)cudaErrorInvalidValue;
   if (mix_terms > 0 && (mix_w == nullptr || mix_out == nullptr || (mix_terms > 1 && hist == nullptr)))
     return (int)cudaErrorInvalidValue;
   // Whole chunks of four that every pointer and pitch lets a thread load at once.
   const int unit = dtype == VX_DTYPE_F32 ? 16 : 8, per = dtype == VX_DTYPE_F32 ? 4 : 2;
   const bool vec = hidden % 4 == 0 && hidden / 4 <= 256 * GV_CHUNKS && aligned_to(resid_in, 16) && aligned_to(resid_out, 16) &&
-                   aligned_to(weight, 16) && aligned_to(delta, unit) && (delta_ld * per) % unit == 0 &&
+                   aligned_to(weight, 16) &&
+                   (delta32 != nullptr ? (aligned_to(delta32, 16) && delta32_ld % 4 == 0)
+                                       : (aligned_to(delta, unit) && (delta_ld * per) % unit == 0)) &&
+                   (delta_bias == nullptr || aligned_to(delta_bias, 16)) &&
                    (gate == nullptr || (aligned_to(gate, unit) && (gate_ld * per) % unit == 0)) &&
                    (lowp_out == nullptr || aligned_to(lowp_out, unit)) &&
                    (mix_terms == 0 || (aligned_to(mix_out, 16) && (hist == nullptr || (aligned_to(hist, 16) && hist_stride % 4 == 0))));
@@ -434,7 +462,8 @@ VX_API int vx_gated_norm_add(const float* resid_in, float* resid_out, const void
     const int per = (chunks + block - 1) / block;
 #define VX_GNA(T, C)                                                                                              \
   launch_gated_norm_add_vec<T, C>(block, resid_in, resid_out, delta, delta_ld, gate, gate_ld, weight, eps, center, \
-                                  lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, num_rows, hidden, stream)
+                                  lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, num_rows, hidden, delta32,    \
+                                  delta32_ld, delta_bias, stream)
     if (dtype == VX_DTYPE_F32) {
       if (per <= 1) VX_GNA(float, 1); else if (per <= 2) VX_GNA(float, 2); else if (per <= 4) VX_GNA(float, 4); else VX_GNA(float, 8);
     } else {
@@ -448,11 +477,12 @@ VX_API int vx_gated_norm_add(const float* resid_in, float* resid_out, const void
   if (dtype == VX_DTYPE_F32)
     launch_pdl(gated_norm_add_kernel<float>, dim3(num_rows), dim3(threads), 0, stream, resid_in, resid_out,
                (const float*)delta, delta_ld, (const float*)gate, gate_ld, weight, eps, center, (float*)lowp_out,
-               hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
+               hist, hist_stride, mix_w, mix_terms, mix_out, hidden, delta32, delta32_ld, delta_bias);
   else
     launch_pdl(gated_norm_add_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), 0, stream, resid_in, resid_out,
                (const __nv_bfloat16*)delta, delta_ld, (const __nv_bfloat16*)gate, gate_ld, weight, eps, center,
-               (__nv_bfloat16*)lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, hidden);
+               (__nv_bfloat16*)lowp_out, hist, hist_stride, mix_w, mix_terms, mix_out, hidden, delta32, delta32_ld,
+               delta_bias);
   return (int)cudaGetLastError();
 }
 

@@ -120,6 +120,9 @@ class StepContext:
     # Columns of a part's first projection that belong to the block around it (a gate over the
     # part's result): rows in the compute dtype, a view of the projection's output; None: none.
     side_output: Optional[torch.Tensor] = None
+    # Set by a block around a part's call when it can take the part's product as float32 sums
+    # (``parts.base.PendingSums``) instead of rows in the compute dtype.
+    takes_pending_sums: bool = False
     # Host copies, for parts that lay out work of their own.
     q_lens_host: List[int] = field(default_factory=list)
     kv_lens_host: List[int] = field(default_factory=list)

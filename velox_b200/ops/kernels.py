@@ -86,7 +86,7 @@ def core():
         lib.vx_norm_rows.argtypes = [_ptr, _ptr, _ptr, _c_f, _c_int, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr]
         lib.vx_gated_norm_add.argtypes = [
             _ptr, _ptr, _ptr, _c_ll, _ptr, _c_ll, _ptr, _c_f, _c_int, _ptr, _c_int, _ptr, _c_ll, _ptr, _c_int, _ptr,
-            _c_int, _c_int, _ptr,
+            _c_int, _c_int, _ptr, _c_ll, _ptr, _ptr,
         ]
         lib.vx_xielu.argtypes = [_ptr, _c_ll, _ptr, _c_int, _c_int, _c_int, _c_f, _c_f, _ptr]
         lib.vx_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
@@ -331,10 +331,17 @@ def gated_norm_add(
     history: Optional[torch.Tensor] = None,
     mix_weights: Optional[torch.Tensor] = None,
     mix_out: Optional[torch.Tensor] = None,
+    sums: Optional[torch.Tensor] = None,
+    sums_bias: Optional[torch.Tensor] = None,
+    compute_dtype: Optional[torch.dtype] = None,
 ) -> None:
     """A sublayer's result joins the float32 stream: ``y = delta * sigmoid(gate)`` (``gate``
     None: ``y = delta``), ``resid_out = resid_in + norm(y) * weight``.  ``delta`` and ``gate``
     are rows in the compute dtype and may be column ranges of wider buffers.
+
+    Instead of ``delta`` the result may lie in ``sums``, float32 rows into which a projection has
+    added its shares (``delta`` None, ``compute_dtype`` given): then ``y`` is made from ``sums +
+    sums_bias`` and the rows read are set to zero again.
 
     With ``mix_weights`` (float32 [n]) what goes on is ``sum_{j < n-1} mix_weights[j] *
     history[j] + mix_weights[n-1] * resid_out`` (``history`` float32 [>= n-1, rows, width]: the
@@ -348,8 +355,22 @@ def gated_norm_add(
         raise ValueError("gated_norm_add: widths do not agree")
     if resid_in.shape[0] < num_rows or resid_out.shape[0] < num_rows:
         raise ValueError(f"gated_norm_add: {num_rows} rows asked for")
-    dtype = delta.dtype
-    delta_ld = _rows_view(delta, "delta", dtype, num_rows, hidden)
+    if (delta is None) == (sums is None):
+        raise ValueError("gated_norm_add takes the result either as delta or as float32 sums")
+    sums_ld = 0
+    if sums is not None:
+        if compute_dtype is None:
+            raise ValueError("gated_norm_add: float32 sums need the compute dtype named")
+        dtype = compute_dtype
+        sums_ld = _rows_view(sums, "sums", torch.float32, num_rows, hidden)
+        delta_ld = 0
+        if sums_bias is not None:
+            _need(sums_bias, torch.float32, "sums_bias")
+            if sums_bias.numel() != hidden:
+                raise ValueError("gated_norm_add: the bias has another width than the rows")
+    else:
+        dtype = delta.dtype
+        delta_ld = _rows_view(delta, "delta", dtype, num_rows, hidden)
     gate_ld = 0 if gate is None else _rows_view(gate, "gate", dtype, num_rows, hidden)
     if lowp_out is not None:
         _need(lowp_out, dtype, "lowp_out")
@@ -372,7 +393,8 @@ def gated_norm_add(
     _check(
         core().vx_gated_norm_add(_p(resid_in), _p(resid_out), _p(delta), delta_ld, _p(gate), gate_ld, _p(weight),
                                  float(eps), 1 if center else 0, _p(lowp_out), _code(dtype), _p(history), hist_stride,
-                                 _p(mix_weights), terms, _p(mix_out), num_rows, hidden, _stream()),
+                                 _p(mix_weights), terms, _p(mix_out), num_rows, hidden, _p(sums), sums_ld,
+                                 _p(sums_bias) if sums is not None else None, _stream()),
         "gated_norm_add",
     )
 

@@ -8,6 +8,7 @@ from .base import (
     Norm,
     PagedCacheSpec,
     Part,
+    PendingSums,
     PositionEncoding,
     StateSpec,
 )
@@ -16,6 +17,6 @@ from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSource, W
 
 __all__ = [
     "CacheNeeds", "FeedForward", "HiddenState", "LayerSpec", "Mixer", "ModelSpec", "Norm",
-    "PagedCacheSpec", "Part", "PartSpec", "PositionEncoding", "ScheduleEntry", "StateSpec",
+    "PagedCacheSpec", "Part", "PartSpec", "PendingSums", "PositionEncoding", "ScheduleEntry", "StateSpec",
     "TensorSource", "WeightSpec", "part_class", "register_part", "unregister_part",
 ]

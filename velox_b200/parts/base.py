@@ -98,6 +98,17 @@ class PendingNorm:
         return self.out
 
 
+@dataclass
+class PendingSums:
+    """A part's product as float32 rows into which its last projection has added its shares (K cut
+    into chunks of independent CTAs): what a block may get from a part instead of a tensor in the
+    compute dtype.  ``bias`` (float32, or None) still has to be added.  The buffer was zero before
+    the projection and whoever reads the rows sets them to zero again."""
+
+    sums: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+
+
 class Part:
     """Base of every part: parameters, weights by local name, compute dtype."""
 

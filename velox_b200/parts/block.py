@@ -11,7 +11,7 @@ import os
 import torch
 
 from ..ops import kernels
-from .base import HiddenState
+from .base import HiddenState, PendingSums
 from .registry import register_part
 
 # VELOX_B200_NO_NORM_FUSION=1 runs every norm as a kernel of its own (for bisecting).
@@ -138,7 +138,9 @@ class PostNormBlock:
         if not last:
             source = work if lowp is None else lowp
             ctx.side_output = None
+            ctx.takes_pending_sums = lowp is not None
             product = self.feed_forward.forward(source, ctx)
+            ctx.takes_pending_sums = False
             self._join(work, work, product, ctx.side_output, self.norm_feed_forward, T, lowp, store, mix_out, True)
         ctx.side_output = None
         hidden.resid = mix_out if self.depth_mix else work
@@ -147,8 +149,12 @@ class PostNormBlock:
 
     def _join(self, resid_in, resid_out, delta, gate, norm, num_rows, lowp, store, mix_out, last) -> None:
         mixing = self.depth_mix and last
+        sums = bias = None
+        if isinstance(delta, PendingSums):
+            sums, bias, delta = delta.sums, delta.bias, None
         kernels.gated_norm_add(
             resid_in, resid_out, delta, gate, norm.weight, norm.eps, norm.center, num_rows, lowp_out=lowp,
             history=store if mixing else None, mix_weights=self.mix_weight if mixing else None,
-            mix_out=mix_out if mixing else None,
+            mix_out=mix_out if mixing else None, sums=sums, sums_bias=bias,
+            compute_dtype=None if sums is None else lowp.dtype,
         )

@@ -11,7 +11,7 @@ import torch
 
 from ..ops import kernels
 from ..ops.linear import DETERMINISTIC, choose_splits, linear, swiglu_linear, use_tensor_core_kernel
-from .base import FeedForward
+from .base import FeedForward, PendingSums
 from .registry import register_part
 
 
@@ -123,6 +123,14 @@ class DenseXielu(FeedForward):
         if not fused:
             linear(x, self.w_up, self.b_up, up, T, self.b_up_lowp, status=ctx.status)
             kernels.xielu(up[:, self.side_rows :], act, T, self.a_pos, self.a_neg)
+        if (getattr(ctx, "takes_pending_sums", False) and ctx.status is not None
+                and use_tensor_core_kernel(act, self.w_down, T)):
+            # Few tokens and a block that can take it: the down projection's K is cut into chunks
+            # of independent CTAs that add their shares into float32 rows (zero before, and set to
+            # zero again by the block's join kernel, which also adds the bias).
+            sums = ws.get("dense.sums", (ws.max_tokens, self.hidden_size), torch.float32)
+            linear(act, self.w_down, None, sums, T, status=ctx.status, accumulate=True)
+            return PendingSums(sums, self.b_down)
         out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(act, self.w_down, self.b_down, out, T, self.b_down_lowp, status=ctx.status)
         return out
