@@ -59,7 +59,27 @@ WIDE = config(256, 500, [
     layer(mixer(8, 32, 32, 32, 96, 0.125, base=250000.0, kv_from=0), 512),
 ], eps=1e-5, cap=15.0)
 
-ALL = {"small": SMALL, "odd": ODD, "wide": WIDE}
+# More heads than an attention tile has rows (20 and 17 on one cached row), so a token's heads
+# are cut across tiles.
+MANY_HEADS = config(160, 300, [
+    layer(mixer(20, 8, 8, 8, 40, 0.3), 96),
+    layer(mixer(17, 16, 8, 12, 40, 0.2, kv_from=0), 64),
+])
+
+# A width that is no multiple of four, an odd vocabulary, odd inner widths, an odd rotated width of
+# which four dims rotate, cached rows of 24 and 11 values; the largest row the attention kernels
+# take (224 + 32 = 256) in a model of its own.
+RAGGED = config(90, 1001, [
+    layer(mixer(3, 10, 5, 7, 19, 0.3, rot_dims=4), 77),
+    layer(mixer(2, 6, 5, 9, 19, 0.3, rot_dims=4, kv_from=0), 33),
+    layer(mixer(5, 12, 2, 3, 9, 0.3), None),
+], cap=5.0)
+LARGEST_ROW = config(192, 257, [
+    layer(mixer(3, 32, 32, 48, 224, 0.1), 200),
+    layer(mixer(2, 64, 32, 16, 224, 0.1, kv_from=0), None),
+])
+
+ALL = {"small": SMALL, "odd": ODD, "wide": WIDE, "many_heads": MANY_HEADS, "ragged": RAGGED, "largest_row": LARGEST_ROW}
 
 
 def make_weights(cfg: Dict[str, Any], seed: int, sharp: float = 1.0) -> Dict[str, torch.Tensor]:

@@ -296,6 +296,26 @@ def test_whole_then_decode_then_portions(models, case, dtype):
     assert replayer.cache.num_free_slots == replayer.max_live
 
 
+@pytest.mark.parametrize("dtype", list(DTYPES))
+@pytest.mark.parametrize("case", ["many_heads", "ragged", "largest_row"])
+def test_other_sizes(tmp_path, case, dtype):
+    """Sizes at the edges of what the kernels take, one request whole, decoded and in portions."""
+    cfg = pc.ALL[case]
+    tensors = pc.make_weights(cfg, seed=3, sharp=1.5)
+    folder = str(tmp_path / case)
+    pc.write_folder(folder, cfg, tensors)
+    tokens = random_prompts(cfg["vocab"], [150], seed=1)[0]
+    ref = plain.forward_logits(tensors, cfg, tokens)
+    replayer = make_replayer(folder, dtype, max_tokens=192, page=16)
+    whole = replay_one(replayer, "w", tokens, [150])
+    decoded = replay_one(replayer, "d", tokens, [120] + [1] * 30)
+    portions = replay_one(replayer, "p", tokens, changing_cuts(150))
+    for what, got in (("whole", whole), ("decoded", decoded), ("portions", portions)):
+        check_logits(got, ref, dtype, f"{case} {what}")
+    if dtype == "float32":
+        assert np.array_equal(whole, decoded) and np.array_equal(whole, portions)
+
+
 def mixed_trace(prompts, rng, max_live=4):
     progress = [0] * len(prompts)
     waiting = list(range(len(prompts)))
@@ -466,7 +486,7 @@ def test_command_lines_take_the_design(tmp_path, capsys):
     assert roofline.main(["--model-size", "tiny-p", "--batch", "2", "--context", "40", "--layers", "1,3", "--steps", "4",
                           "--warmup", "1", "--block-size", "8", "--output-json", str(table)]) == 0
     rows = json.loads(table.read_text())
-    assert rows[0]["us_by_bytes"] > 0 and rows[0]["size"] == "tiny-p"
+    assert rows[0]["us_per_layer"] > 0 and 0 < rows[0]["cache_share"] < 1 and rows[0]["size"] == "tiny-p"
 
 
 def test_greedy_generation_through_the_engine(models):
