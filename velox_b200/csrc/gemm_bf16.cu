@@ -237,19 +237,16 @@ __device__ __forceinline__ void store_output(const GemmArgs& g, size_t index, fl
     asm volatile("red.global.add.f32 [%0], %1;" ::"l"((float*)g.out + index), "f"(value) : "memory");
 }
 
-// The same for a launch that knows token and column (all modes that reach store_output, and 5).
-__device__ __forceinline__ void store_output_at(const GemmArgs& g, int t, int n, float value) {
-  if (g.mode == 5) {
-    if (n < g.act_from) {
-      ((__nv_bfloat16*)g.out)[(size_t)t * g.ldy + n] = __float2bfloat16_rn(value);
-    } else {
-      const float z = value;
-      const float v = z > 0.f ? fmaf(g.a_pos * z, z, 0.5f * z) : fmaf(g.a_neg, (__expf(z) - 1.0f) - z, 0.5f * z);
-      ((__nv_bfloat16*)g.act_out)[(size_t)t * g.act_ld + (n - g.act_from)] = __float2bfloat16_rn(v);
-    }
-    return;
+// Mode 5 (kernels instantiated with ACT only, so that the other modes' epilogues are what they
+// were): one element, to the plain columns or, activated, to the second buffer.
+__device__ __forceinline__ void store_activated(const GemmArgs& g, int t, int n, float value) {
+  if (n < g.act_from) {
+    ((__nv_bfloat16*)g.out)[(size_t)t * g.ldy + n] = __float2bfloat16_rn(value);
+  } else {
+    const float z = value;
+    const float v = z > 0.f ? fmaf(g.a_pos * z, z, 0.5f * z) : fmaf(g.a_neg, (__expf(z) - 1.0f) - z, 0.5f * z);
+    ((__nv_bfloat16*)g.act_out)[(size_t)t * g.act_ld + (n - g.act_from)] = __float2bfloat16_rn(v);
   }
-  store_output(g, (size_t)t * g.ldy + n, value);
 }
 
 constexpr int GB_MAX_SPLITS = 8;  // CTAs of a cluster (a portable one; the device holds too few clusters of sixteen)
@@ -278,7 +275,7 @@ struct GemmShape {
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024;
 };
 
-template <int BN, int STAGES_>
+template <int BN, int STAGES_, bool ACT = false>
 __global__ void __launch_bounds__(GB_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                  const __grid_constant__ CUtensorMap map_x, GemmArgs g) {
@@ -567,7 +564,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           if (n < g.N) {
             for (int j = 0; j < cols; ++j) {
               const int t = t0 + c0 + j;
-              if (t < g.T) store_output_at(g, t, n, v[j] * (normed ? ssq_s[c0 + j] : 1.0f) + b);
+              if (t < g.T) {
+                const float value = v[j] * (normed ? ssq_s[c0 + j] : 1.0f) + b;
+                if constexpr (ACT) store_activated(g, t, n, value);
+                else store_output(g, (size_t)t * g.ldy + n, value);
+              }
             }
           }
         }
@@ -696,7 +697,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         for (int peer = 0; peer < g.splits; ++peer)
           acc += recv[((size_t)peer * rows_per_cta + rl) * S::RECV_ROW + j];
         if (normed) acc *= ssq_s[j];
-        store_output_at(g, t, n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
+        if constexpr (ACT) store_activated(g, t, n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
+        else store_output(g, (size_t)t * g.ldy + n, acc + (g.bias != nullptr ? g.bias[n] : 0.f));
       }
     }
     VX_TRACE_MARK(3);
@@ -779,7 +781,7 @@ static int device_sm_count() {
 
 // `one_wave`: launch only if all the grid's clusters are resident at once with this variant's
 // shared memory (-2 otherwise: the caller takes the variant of which an SM holds two CTAs).
-template <int BN, int STAGES_>
+template <int BN, int STAGES_, bool ACT = false>
 static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUtensorMap& mx,
                        const GemmArgs& g, dim3 grid, cudaStream_t stream, bool one_wave = false) {
   using S = GemmShape<BN, STAGES_>;
@@ -787,10 +789,10 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
   static int dynamic_limit = 0;
   if (dynamic_limit == 0) {
     cudaFuncAttributes attributes_of;
-    cudaError_t e = cudaFuncGetAttributes(&attributes_of, gemm_bf16_kernel<BN, STAGES_>);
+    cudaError_t e = cudaFuncGetAttributes(&attributes_of, gemm_bf16_kernel<BN, STAGES_, ACT>);
     if (e != cudaSuccess) return (int)e;
     const int limit = 227 * 1024 - (int)attributes_of.sharedSizeBytes;
-    e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES_>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, STAGES_, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              limit);
     if (e != cudaSuccess) return (int)e;
     dynamic_limit = limit;
@@ -871,7 +873,7 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
       auto it = held.find(key);
       if (it == held.end()) {
         int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_kernel<BN, STAGES_>, &config) != cudaSuccess) {
+        if (cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_kernel<BN, STAGES_, ACT>, &config) != cudaSuccess) {
           (void)cudaGetLastError();
           clusters = 0;
         }
@@ -882,7 +884,7 @@ static int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mw2, const CUte
     const long long clusters_wanted = (long long)grid.x * grid.y;
     if (active > 0 && clusters_wanted > active) return -2;
   }
-  return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN, STAGES_>, mw, mw2, mx, launched);
+  return (int)cudaLaunchKernelEx(&config, gemm_bf16_kernel<BN, STAGES_, ACT>, mw, mw2, mx, launched);
 }
 
 
@@ -1334,6 +1336,16 @@ static int gemm_bf16(const void* x, int x_rows, const float* resid, long long re
   // A grid that gives an SM one CTA at most keeps more tiles in flight per CTA instead.
   const bool deep = bn <= 32 && g.kb_per_split > 4 &&
                     (long long)grid.x * grid.y * grid.z <= (long long)sm_count();
+  if (mode == 5) {
+    // The activation epilogue is a variant of its own (one ring depth per tile width).
+    switch (bn) {
+      case 16: return launch_gemm<16, 4, true>(mw, mw2, mx, g, grid, stream);
+      case 32: return launch_gemm<32, 4, true>(mw, mw2, mx, g, grid, stream);
+      case 64: return launch_gemm<64, 4, true>(mw, mw2, mx, g, grid, stream);
+      case 128: return launch_gemm<128, 4, true>(mw, mw2, mx, g, grid, stream);
+      default: return launch_gemm<256, 4, true>(mw, mw2, mx, g, grid, stream);
+    }
+  }
   switch (bn) {
     case 16: {
       const int code = deep ? launch_gemm<16, 8>(mw, mw2, mx, g, grid, stream, true) : -2;
