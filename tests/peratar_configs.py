@@ -55,9 +55,9 @@ ODD = config(128, 331, [
 # tensor-memory attention kernel and decoded tokens on clusters; unrotated, rotated and value
 # widths all equal.
 WIDE = config(256, 500, [
-    layer(mixer(8, 32, 32, 32, 96, 0.125, base=250000.0), 512),
-    layer(mixer(8, 32, 32, 32, 96, 0.125, base=250000.0, kv_from=0), 512),
-], eps=1e-5, cap=15.0)
+    layer(mixer(8, 32, 32, 32, 96, 0.125, base=1000000.0), 512),
+    layer(mixer(8, 32, 32, 32, 96, 0.125, base=1000000.0, kv_from=0), 512),
+], eps=2e-5, cap=25.0)
 
 # More heads than an attention tile has rows (20 and 17 on one cached row), so a token's heads
 # are cut across tiles.
