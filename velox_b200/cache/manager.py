@@ -34,6 +34,8 @@ class CacheGroup:
 
     name: str
     window: Optional[int] = None
+    # Keys 0 .. keep_first - 1 are never passed by the window: their pages are kept.
+    keep_first: int = 0
 
 
 @dataclass
@@ -153,7 +155,9 @@ class CacheManager:
                 continue
             dead_blocks = min(first_needed // self.page_size, len(seq.tables[index]))
             table = seq.tables[index]
-            for block in range(seq.first_live[index], dead_blocks):
+            # Pages that hold kept first keys stay: what is given back starts behind them.
+            kept_blocks = -(-group.keep_first // self.page_size) if group.keep_first > 0 else 0
+            for block in range(max(seq.first_live[index], kept_blocks), dead_blocks):
                 self.allocators[index].give_back(table[block])
                 table[block] = NULL_PAGE
                 seq.tables_version += 1
@@ -163,12 +167,21 @@ class CacheManager:
         """Give back every page the sequence still holds and forget its tables."""
         for index, alloc in enumerate(self.allocators):
             table = seq.tables[index]
-            for block in range(seq.first_live[index], len(table)):
+            for block in self._held_blocks(seq, index):
                 alloc.give_back(table[block])
             seq.tables[index] = []
             seq.first_live[index] = 0
         seq.tables_version += 1
         self._live.pop(seq.seq_id, None)
+
+    def _held_blocks(self, seq: SequenceCache, index: int) -> List[int]:
+        """Logical blocks of group ``index`` whose pages the sequence still holds: those from
+        ``first_live`` on and, before it, the ones that hold kept first keys."""
+        group = self.groups[index]
+        count = len(seq.tables[index])
+        first = seq.first_live[index]
+        kept = min(-(-group.keep_first // self.page_size), first, count) if group.keep_first > 0 else 0
+        return list(range(0, kept)) + list(range(first, count))
 
     def reset_for_recompute(self, seq: SequenceCache) -> None:
         """Preemption by recompute: drop the pages and start over from token 0."""
@@ -225,7 +238,8 @@ class CacheManager:
             seen: Dict[int, str] = {}
             for seq in self._live.values():
                 table = seq.tables[index]
-                for block in range(seq.first_live[index], len(table)):
+                held = self._held_blocks(seq, index)
+                for block in held:
                     page = table[block]
                     if page == NULL_PAGE:
                         raise AssertionError(f"{seq.seq_id}: live block {block} is the null page")
@@ -237,7 +251,7 @@ class CacheManager:
                     if alloc.holders(page) != 1:
                         raise AssertionError(f"page {page} has {alloc.holders(page)} holders")
                     seen[page] = seq.seq_id
-                for block in range(0, seq.first_live[index]):
+                for block in sorted(set(range(0, seq.first_live[index])) - set(held)):
                     if table[block] != NULL_PAGE:
                         raise AssertionError(f"{seq.seq_id}: released block {block} still names a page")
             if len(seen) != alloc.num_used:

@@ -359,6 +359,261 @@ class PeratarConfig(ModelConfig):
         return out
 
 
+def _window(cfg: Mapping[str, Any], where: str, keep_allowed: bool) -> Tuple[int, int]:
+    mask = _mapping(cfg, "mask", where)
+    size = _count(mask, "size", where + ".mask")
+    keep = mask.get("keep_first", 0)
+    if isinstance(keep, bool) or not isinstance(keep, int) or keep < 0:
+        raise ConfigError(f"{where}.mask: keep_first={keep!r} must be a non-negative integer")
+    if keep and not keep_allowed:
+        raise ConfigError(f"{where}.mask: keep_first is not a key of this mixer")
+    return size, keep
+
+
+@dataclass(frozen=True)
+class WindowAttentionConfig:
+    """Softmax attention with grouped heads over a sliding window.  ``keep_first`` keys stay
+    visible behind the window; ``rot`` (or None) = (base, dims, scaling or None) with scaling =
+    (factor, original, fast, slow); ``biases``, ``sink`` and ``head_gate`` say which further
+    tensors the mixer has."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int
+    keep_first: int = 0
+    rot: Optional[Tuple[float, int, Optional[Tuple[float, float, float, float]]]] = None
+    biases: bool = False
+    sink: bool = False
+    head_gate: bool = False
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str, *, rotated: bool, biases: bool, sink: bool, head_gate: bool,
+              keep_allowed: bool) -> "WindowAttentionConfig":
+        heads, kv_heads = _count(m, "heads", where), _count(m, "kv_heads", where)
+        if heads % kv_heads:
+            raise ConfigError(f"{where}: heads={heads} must be a multiple of kv_heads={kv_heads}")
+        window, keep = _window(m, where, keep_allowed)
+        rot = None
+        if rotated:
+            r = _mapping(m, "rot", where)
+            dims = _count(r, "dims", where + ".rot")
+            dim = _count(m, "dim", where)
+            if dims % 2 or dims > dim:
+                raise ConfigError(f"{where}.rot: dims={dims} must be even and at most dim={dim}")
+            scaling = None
+            if r.get("scaling") is not None:
+                sc = _mapping(r, "scaling", where + ".rot")
+                scaling = tuple(_number(sc, key, where + ".rot.scaling") for key in ("factor", "original", "fast", "slow"))
+                if scaling[0] <= 0 or scaling[1] <= 0 or scaling[2] <= 0 or scaling[3] <= 0:
+                    raise ConfigError(f"{where}.rot.scaling: factor, original, fast and slow must be positive")
+            rot = (_number(r, "base", where + ".rot"), dims, scaling)
+        elif m.get("rot") is not None:
+            raise ConfigError(f"{where}: this mixer has no rotation, but 'rot' is given")
+        return WindowAttentionConfig(
+            heads=heads, kv_heads=kv_heads, dim=_count(m, "dim", where), vdim=_count(m, "vdim", where),
+            scale=_number(m, "scale", where), window=window, keep_first=keep, rot=rot, biases=biases, sink=sink,
+            head_gate=head_gate)
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        mask: Dict[str, Any] = {"size": self.window}
+        if self.keep_first:
+            mask["keep_first"] = self.keep_first
+        out: Dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim,
+                               "scale": self.scale, "mask": mask}
+        if self.rot is not None:
+            base, dims, scaling = self.rot
+            out["rot"] = {"base": base, "dims": dims}
+            if scaling is not None:
+                out["rot"]["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+        return out
+
+
+@dataclass(frozen=True)
+class RecurrenceConfig:
+    """The gated linear recurrence: ``width`` channels in ``blocks`` parts, a convolution of
+    ``conv`` taps."""
+
+    width: int
+    blocks: int
+    conv: int
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "RecurrenceConfig":
+        out = RecurrenceConfig(width=_count(m, "width", where), blocks=_count(m, "blocks", where),
+                               conv=_count(m, "conv", where))
+        if out.width % out.blocks:
+            raise ConfigError(f"{where}: width={out.width} must be a multiple of blocks={out.blocks}")
+        return out
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        return {"width": self.width, "blocks": self.blocks, "conv": self.conv}
+
+
+@dataclass(frozen=True)
+class StateSpaceConfig:
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    norm_groups: int
+    conv: int
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "StateSpaceConfig":
+        out = StateSpaceConfig(heads=_count(m, "heads", where), vdim=_count(m, "vdim", where),
+                               state=_count(m, "state", where), groups=_count(m, "groups", where),
+                               norm_groups=_count(m, "norm_groups", where), conv=_count(m, "conv", where))
+        if out.heads % out.groups:
+            raise ConfigError(f"{where}: heads={out.heads} must be a multiple of groups={out.groups}")
+        if (out.heads * out.vdim) % out.norm_groups:
+            raise ConfigError(f"{where}: heads * vdim must be a multiple of norm_groups={out.norm_groups}")
+        return out
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        return {"heads": self.heads, "vdim": self.vdim, "state": self.state, "groups": self.groups,
+                "norm_groups": self.norm_groups, "conv": self.conv}
+
+
+@dataclass(frozen=True)
+class RedalixFeedForwardConfig:
+    """``kind`` dense: ``ff``.  ``kind`` moe: ``experts`` of inner width ``expert_ff``, ``top`` per
+    token, and ``shared_ff`` (None: no shared expert)."""
+
+    kind: str
+    ff: int = 0
+    experts: int = 0
+    top: int = 0
+    expert_ff: int = 0
+    shared_ff: Optional[int] = None
+
+    @staticmethod
+    def parse(m: Mapping[str, Any], where: str) -> "RedalixFeedForwardConfig":
+        kind = m.get("kind")
+        if kind == "dense":
+            return RedalixFeedForwardConfig(kind="dense", ff=_count(m, "ff", where))
+        if kind == "moe":
+            router = _mapping(m, "router", where)
+            experts, top = _count(router, "experts", where + ".router"), _count(router, "top", where + ".router")
+            if top > experts:
+                raise ConfigError(f"{where}.router: top={top} is more than experts={experts}")
+            shared = m.get("shared")
+            return RedalixFeedForwardConfig(
+                kind="moe", experts=experts, top=top,
+                expert_ff=_count(_mapping(m, "expert", where), "ff", where + ".expert"),
+                shared_ff=None if shared is None else _count(_mapping(m, "shared", where), "ff", where + ".shared"))
+        raise ConfigError(f"{where}: mlp kind {kind!r} is not supported ('dense' and 'moe' are)")
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        if self.kind == "dense":
+            return {"kind": "dense", "ff": self.ff}
+        out: Dict[str, Any] = {"kind": "moe", "expert": {"ff": self.expert_ff},
+                               "router": {"experts": self.experts, "top": self.top}}
+        if self.shared_ff is not None:
+            out["shared"] = {"ff": self.shared_ff}
+        return out
+
+
+@dataclass(frozen=True)
+class RedalixLayerConfig:
+    """``type`` parallel: ``left`` (attention) and ``right`` (recurrence); attention: ``left``;
+    mamba2: ``state_space``."""
+
+    type: str
+    left: Optional[WindowAttentionConfig] = None
+    right: Optional[RecurrenceConfig] = None
+    state_space: Optional[StateSpaceConfig] = None
+    mlp: Optional[RedalixFeedForwardConfig] = None
+
+
+@dataclass(frozen=True)
+class RedalixConfig(ModelConfig):
+    """``Redalix``: every layer is ``x <- x + mixer(h) + ff(h)`` with ``h = rms_norm(x)``; the
+    mixer is windowed attention with rotation, biases and a gate per head (``attention``), a
+    state-space layer (``mamba2``), or windowed attention with a sink and kept first keys beside
+    a gated linear recurrence (``parallel``); the feed-forward is dense or a set of experts
+    chosen by a table over token ids, with a gated shared expert.  config.json keys: ``vocab``,
+    ``width``, ``norm.eps`` and ``layers`` (a list of ``{type, mixer, mlp}``)."""
+
+    layers: Tuple[RedalixLayerConfig, ...] = ()
+    norm_eps: float = 1e-5
+    torch_dtype: str = "bfloat16"
+
+    @staticmethod
+    def from_dict(cfg: Mapping[str, Any]) -> "RedalixConfig":
+        name = cfg.get("architecture") or (cfg.get("architectures") or ["Redalix"])[0]
+        raw_layers = cfg.get("layers")
+        if not isinstance(raw_layers, (list, tuple)) or not raw_layers:
+            raise ConfigError("config.json key 'layers' must be a non-empty list")
+        layers = []
+        for index, raw in enumerate(raw_layers):
+            where = f"config.json layers[{index}]"
+            if not isinstance(raw, Mapping):
+                raise ConfigError(f"{where} must be an object")
+            kind = raw.get("type")
+            m = _mapping(raw, "mixer", where)
+            mlp = None
+            if raw.get("mlp") is not None:
+                mlp = RedalixFeedForwardConfig.parse(_mapping(raw, "mlp", where), where + ".mlp")
+            if kind == "parallel":
+                layer = RedalixLayerConfig(
+                    type=kind,
+                    left=WindowAttentionConfig.parse(_mapping(m, "left", where + ".mixer"), where + ".mixer.left",
+                                                     rotated=False, biases=False, sink=True, head_gate=False,
+                                                     keep_allowed=True),
+                    right=RecurrenceConfig.parse(_mapping(m, "right", where + ".mixer"), where + ".mixer.right"),
+                    mlp=mlp)
+            elif kind == "attention":
+                layer = RedalixLayerConfig(
+                    type=kind,
+                    left=WindowAttentionConfig.parse(m, where + ".mixer", rotated=True, biases=True, sink=False,
+                                                     head_gate=True, keep_allowed=False),
+                    mlp=mlp)
+            elif kind == "mamba2":
+                layer = RedalixLayerConfig(type=kind, state_space=StateSpaceConfig.parse(m, where + ".mixer"), mlp=mlp)
+            else:
+                raise ConfigError(f"{where}: layer type {kind!r} is not supported "
+                                  "('parallel', 'attention' and 'mamba2' are)")
+            layers.append(layer)
+        eos = cfg.get("eos_token_id")
+        eos_ids: Tuple[int, ...] = () if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(t) for t in eos))
+        return RedalixConfig(
+            architecture=str(name),
+            vocab_size=_count(cfg, "vocab", "config.json"),
+            hidden_size=_count(cfg, "width", "config.json"),
+            num_hidden_layers=len(layers),
+            max_position_embeddings=int(cfg.get("max_position_embeddings", 1 << 20)),
+            tie_word_embeddings=False,
+            eos_token_ids=eos_ids,
+            layers=tuple(layers),
+            norm_eps=_number(_mapping(cfg, "norm", "config.json"), "eps", "config.json norm"),
+            torch_dtype=str(cfg.get("torch_dtype", "bfloat16")),
+        )
+
+    def to_json_dict(self) -> Dict[str, Any]:
+        layers = []
+        for layer in self.layers:
+            if layer.type == "parallel":
+                mixer: Dict[str, Any] = {"left": layer.left.to_json_dict(), "right": layer.right.to_json_dict()}
+            elif layer.type == "attention":
+                mixer = layer.left.to_json_dict()
+            else:
+                mixer = layer.state_space.to_json_dict()
+            layers.append({"type": layer.type, "mixer": mixer,
+                           "mlp": None if layer.mlp is None else layer.mlp.to_json_dict()})
+        out: Dict[str, Any] = {
+            "architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+            "norm": {"eps": self.norm_eps}, "layers": layers, "torch_dtype": self.torch_dtype,
+        }
+        if self.max_position_embeddings != 1 << 20:
+            out["max_position_embeddings"] = self.max_position_embeddings
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out
+
+
 def read_config_json(model_dir: str) -> Dict[str, Any]:
     path = os.path.join(model_dir, "config.json")
     if not os.path.isfile(path):

@@ -22,7 +22,7 @@
 //   otherwise partial rows go to partial_base + kv_head * row_count + r, and merge_index names
 //   the merge item that lists all splits of the same rows.
 // Visibility of key n to a row whose token is at absolute position pos:
-//   kv_begin <= n < kv_end, n <= pos, and n > pos - window when window > 0.
+//   kv_begin <= n < kv_end, n <= pos, and (n > pos - window or n < keep_first) when window > 0.
 // Key tiles start at multiples of the tile width from position 0, whatever kv_begin is, so the
 // float32 result of an unsplit row does not depend on how the prompt was cut into portions.
 //
@@ -86,13 +86,18 @@ struct AttnArgs {
   int* split_counters;      // [m * G], zero between steps; null: a separate kernel merges
   int q_stride, out_stride, table_stride;
   int num_kv_heads, group, page_size, window;
+  // Keys 0 .. keep_first - 1 stay visible behind the window (0: none are kept).
+  int keep_first;
+  // Merge kernel only: one number per query head (natural-log units) whose exponential joins
+  // the softmax denominator with no key and no value; null: none.
+  const float* sinks;
   // Narrow bf16 family: CTAs of a thread-block cluster that share one work item (1, 2, 4, 8).
   int cluster;
   float scale_log2;  // softmax scale * log2(e)
 };
 
-__device__ __forceinline__ bool key_visible(int n, int pos, int kv_begin, int kv_end, int window) {
-  return n >= kv_begin && n < kv_end && n <= pos && (window <= 0 || n > pos - window);
+__device__ __forceinline__ bool key_visible(int n, int pos, int kv_begin, int kv_end, int window, int keep_first) {
+  return n >= kv_begin && n < kv_end && n <= pos && (window <= 0 || n > pos - window || n < keep_first);
 }
 
 // =============================================================================================
@@ -180,7 +185,7 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnArgs a) {
       for (int d = 0; d < D; ++d) s = fmaf(q_s[r][d], k_s[lane][d], s);
       s *= a.scale_log2;
       const int n = n0 + lane;
-      if (!key_visible(n, pos[i], kv_begin, kv_end, a.window)) s = -CUDART_INF_F;
+      if (!key_visible(n, pos[i], kv_begin, kv_end, a.window, a.keep_first)) s = -CUDART_INF_F;
       const float m_new = fmaxf(m[i], warp_max(s));
       const float m_safe = m_new == -CUDART_INF_F ? 0.f : m_new;
       const float p = exp2f(s - m_safe);
@@ -469,7 +474,7 @@ __device__ __forceinline__ void warp_pv(float (&o)[D / 8][4], const float (&p)[N
 template <int NT>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[D / 8][4],
                                              float (&m)[2], float (&l)[2], const int (&pos)[2],
-                                             int nbase, int kv_begin, int kv_end, int window,
+                                             int nbase, int kv_begin, int kv_end, int window, int keep_first,
                                              float scale_log2, int lane) {
   float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
@@ -479,7 +484,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[D / 8
       const int n = nbase + j * 8 + 2 * (lane & 3) + (e & 1);
       const int h = e >> 1;
       float v = s[j][e] * scale_log2;
-      if (pos[h] < 0 || !key_visible(n, pos[h], kv_begin, kv_end, window)) v = -CUDART_INF_F;
+      if (pos[h] < 0 || !key_visible(n, pos[h], kv_begin, kv_end, window, keep_first)) v = -CUDART_INF_F;
       s[j][e] = v;
       mx[h] = fmaxf(mx[h], v);
     }
@@ -568,6 +573,13 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, const int* item, in
     for (int s = threadIdx.x; s < splits; s += 32)
       mt = fmaxf(mt, __ldcg(&a.partial_lse[base + (size_t)s * stride]));
     mt = warp_max(mt);
+    // A sink joins the denominator once, with no value: exp(sink) in the splits' log2 units.
+    float sink = -CUDART_INF_F;
+    if (a.sinks != nullptr) {
+      const int row_ = row_begin + r;
+      sink = a.sinks[kvh * a.group + (row_ - (row_ / a.group) * a.group)] * 1.4426950408889634f;
+      mt = fmaxf(mt, sink);
+    }
     const float m_safe = mt == -CUDART_INF_F ? 0.f : mt;
     float den = 0.f;
     for (int s = threadIdx.x; s < splits; s += 32) {
@@ -577,6 +589,7 @@ __device__ __forceinline__ void merge_row(const AttnArgs& a, const int* item, in
       den += w;
     }
     den = warp_sum(den);
+    if (sink != -CUDART_INF_F) den += exp2f(sink - m_safe);
     if (threadIdx.x == 0) *denom_s = den;
   }
   __syncthreads();
@@ -980,7 +993,7 @@ __global__ void __launch_bounds__(128) attn_wide_kernel(const __grid_constant__ 
       const __nv_bfloat16* v_s = k_s + TILE;
       float s[NT][4];
       warp_qk<NT>(s, q_s + row0 * B_LD, k_s, 0, lane);
-      softmax_step<NT>(s, o, m, l, pos, n0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+      softmax_step<NT>(s, o, m, l, pos, n0, kv_begin, kv_end, a.window, a.keep_first, a.scale_log2, lane);
       warp_pv<NT>(o, s, v_s, 0, lane);
     }
     __syncthreads();  // everyone is done with this stage before it is refilled
@@ -1068,7 +1081,7 @@ struct NarrowWarp {
 
   // Keys [n0 + key0, n0 + key0 + 16) of the tile in k_s / v_s.
   __device__ __forceinline__ void tile(const __nv_bfloat16* k_s, const __nv_bfloat16* v_s, int key0,
-                                       int nbase, int kv_begin, int kv_end, int window,
+                                       int nbase, int kv_begin, int kv_end, int window, int keep_first,
                                        float scale_log2, int lane) {
     float s[NR][4];
 #pragma unroll
@@ -1107,7 +1120,7 @@ struct NarrowWarp {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int p = pos[j][e & 1];
-          if (p >= 0 && !key_visible(nbase + g + 8 * (e >> 1), p, kv_begin, kv_end, window))
+          if (p >= 0 && !key_visible(nbase + g + 8 * (e >> 1), p, kv_begin, kv_end, window, keep_first))
             s[j][e] = -CUDART_INF_F;
         }
     }
@@ -1401,7 +1414,7 @@ __global__ void __launch_bounds__(NARROW_THREADS) attn_narrow_kernel(const __gri
         if (t == group) VX_TRACE_MARK(2);
         if (alive) {
           const __nv_bfloat16* k_s = kv_s + st * 2 * TILE;
-          state.tile(k_s, k_s + TILE, key0, n0 + key0, kv_begin, kv_end, a.window, a.scale_log2, lane);
+          state.tile(k_s, k_s + TILE, key0, n0 + key0, kv_begin, kv_end, a.window, a.keep_first, a.scale_log2, lane);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&kv_empty[st]));  // this warp has read the stage
@@ -1982,6 +1995,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
     // The keys this row sees are vis_lo <= n < vis_lo + vis_span (none for a row past the end).
     const int vis_lo = max(kv_begin, a.window > 0 ? pos - a.window + 1 : 0);
     const unsigned vis_span = pos < 0 ? 0u : (unsigned)max(0, min(kv_end, pos + 1) - vis_lo);
+    // The kept first keys it sees besides: kv_begin <= n < kv_begin + keep_span.
+    const unsigned keep_span = (pos < 0 || a.keep_first <= 0)
+                                   ? 0u
+                                   : (unsigned)max(0, min(min(a.keep_first, kv_end), pos + 1) - kv_begin);
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
 #ifdef VX_TRACE
     // Cycles of the softmax threads' four phases, summed over the tiles (thread 0 reports them
@@ -2019,9 +2036,10 @@ __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1) attn_tc_ke
                                 (a.window <= 0 || n0 > pos - a.window);
       if (!__all_sync(0xffffffffu, row_sees_all)) {
         const int rel = n0 - vis_lo;  // one unsigned compare per key: rel + i in [0, vis_span)
+        const int rel_keep = n0 - kv_begin;
 #pragma unroll
         for (int i = 0; i < B_BN; ++i)
-          if ((unsigned)(rel + i) >= vis_span) s[i] = -CUDART_INF_F;
+          if ((unsigned)(rel + i) >= vis_span && (unsigned)(rel_keep + i) >= keep_span) s[i] = -CUDART_INF_F;
       }
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
@@ -2218,7 +2236,7 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
                           float* partial_lse, const int* merge_items, int* split_counters,
                           int q_stride, int out_stride, int table_stride,
                           int num_kv_heads, int group, int page_size, int window,
-                          float softmax_scale) {
+                          float softmax_scale, int keep_first = 0) {
   AttnArgs a;
   memset(&a, 0, sizeof(a));
   a.q = q;
@@ -2243,6 +2261,8 @@ static AttnArgs make_args(const void* q, void* out, const void* k_cache, const v
   a.group = group;
   a.page_size = page_size;
   a.window = window;
+  a.keep_first = window > 0 ? keep_first : 0;
+  a.sinks = nullptr;
   a.cluster = 1;
   a.scale_log2 = softmax_scale * 1.4426950408889634f;
   return a;
@@ -2269,7 +2289,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
                         int* status, float* partial_o, float* partial_lse, const int* merge_items,
                         int* split_counters, int q_stride, int out_stride, int table_stride,
                         int num_kv_heads, int group, int page_size, long long num_pages,
-                        int window, float softmax_scale, int cluster, cudaStream_t stream) {
+                        int window, float softmax_scale, int cluster, int keep_first, cudaStream_t stream) {
   if (num_items <= 0) return 0;
   // Only the narrow bf16 family shares an item among the CTAs of a cluster; for the
   // tensor-memory family 2 means "two CTAs on an SM" (see its launch below).
@@ -2281,7 +2301,7 @@ VX_API int vx_attention(int kind, const void* q, void* out, const void* k_cache,
   AttnArgs a = make_args(q, out, k_cache, v_cache, block_tables, q_start, q_len, kv_len,
                                items, status, partial_o, partial_lse, merge_items, split_counters,
                                q_stride, out_stride, table_stride,
-                               num_kv_heads, group, page_size, window, softmax_scale);
+                               num_kv_heads, group, page_size, window, softmax_scale, keep_first);
   if (kind != 0 && TMA_KV) {
     // Page sizes are powers of two: a 64-key tile is whole pages, or lies inside one page.
     if (page_size <= 0 || (page_size & (page_size - 1)) != 0) return -1;
@@ -2440,11 +2460,12 @@ VX_API int vx_attn_narrow_max_active_clusters(int cluster) {
 VX_API int vx_attention_merge(int dtype, void* out, const int* q_start, const int* merge_items,
                               int num_items, int max_rows, const float* partial_o,
                               const float* partial_lse, int out_stride, int num_kv_heads,
-                              int group, cudaStream_t stream) {
+                              int group, const float* sinks, cudaStream_t stream) {
   if (num_items <= 0 || max_rows <= 0) return 0;
   AttnArgs a = make_args(nullptr, out, nullptr, nullptr, nullptr, q_start, nullptr, nullptr,
                          nullptr, nullptr, const_cast<float*>(partial_o), const_cast<float*>(partial_lse),
                          merge_items, nullptr, 0, out_stride, 0, num_kv_heads, group, 1, 0, 1.0f);
+  a.sinks = sinks;
   const dim3 grid(num_items, num_kv_heads, max_rows);
   const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
   if (dtype == VX_DTYPE_F32)

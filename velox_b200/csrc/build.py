@@ -1,8 +1,9 @@
 """Compiles the CUDA sources of this directory for sm_100a and loads them with ctypes.
 
-There are two libraries: ``core`` (row-wise kernels, sampling, GEMMs; one build) and
-``attention`` (one build per head size, ``-DVX_HEAD_DIM=<D>``), so a process compiles what its
-model needs and nothing else.  A build is keyed by a hash of its sources, flags and compiler
+There are three libraries: ``core`` (row-wise kernels, sampling, GEMMs; one build),
+``attention`` (one build per head size, ``-DVX_HEAD_DIM=<D>``) and ``mixers`` (recurrent mixers
+and expert feed-forwards; one build), so a process compiles what its model needs and nothing
+else.  A build is keyed by a hash of its sources, flags and compiler
 version; it is made once and reused.  Builds go to ``velox_b200/_build`` inside the package when
 that is writable, else to ``$VELOX_B200_BUILD_DIR``, else to a per-user folder under the
 system's temporary directory.  nvcc cross-compiles without a GPU, so the build also runs on a
@@ -35,6 +36,9 @@ if os.environ.get("VELOX_B200_TRACE") == "1":
     COMMON_FLAGS = COMMON_FLAGS + ["-DVX_TRACE"]
 
 CORE_SOURCES = ("core.cu", "sampling.cu", "gemm_bf16.cu", "residual.cu", "latent.cu")
+# Mixers with a state of fixed size per request and feed-forwards with experts: built only for
+# models that have such parts.
+MIXER_SOURCES = ("sequence.cu", "routed.cu")
 ATTENTION_SOURCES = ("attention.cu",)
 HEADERS = ("common.cuh", "attention_static.h")
 
@@ -183,6 +187,10 @@ def load_core() -> ctypes.CDLL:
     return _load("core", CORE_SOURCES, ())
 
 
+def load_mixers() -> ctypes.CDLL:
+    return _load("mixers", MIXER_SOURCES, ())
+
+
 def load_attention(head_dim: int) -> ctypes.CDLL:
     if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
         raise ValueError(
@@ -207,7 +215,7 @@ def _load(name: str, sources: Sequence[str], defines: Sequence[str]) -> ctypes.C
 
 def build_all(head_dims: Iterable[int] = (128,)) -> List[str]:
     """Compile every library (for the given head sizes) without loading anything."""
-    paths = [build_library("core", CORE_SOURCES, ())]
+    paths = [build_library("core", CORE_SOURCES, ()), build_library("mixers", MIXER_SOURCES, ())]
     for head_dim in head_dims:
         paths.append(
             build_library(f"attention_d{head_dim}", ATTENTION_SOURCES, (f"-DVX_HEAD_DIM={head_dim}",))

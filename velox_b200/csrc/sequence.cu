@@ -1,0 +1,579 @@
+// Kernels of mixers that carry a state of fixed size from token to token, and the row-wise
+// kernels around them.
+//
+//   pair_rope_cache_write_kernel  neighbouring pairs (2i, 2i+1) of q and k turn by tabulated
+//                                 angles; k and v go to their cache slots; the projection's row
+//                                 may hold further columns behind q | k | v
+//   head_gate_kernel              out[t, h, :] *= sigmoid(logit[t, h])
+//   conv_tokens_kernel            causal convolution per channel over a sequence's tokens, the
+//                                 taps before the portion's first token taken from the state
+//   conv_state_update_kernel      the last taps - 1 inputs of every sequence into its state
+//   rglru_gates_kernel            block-diagonal gate matrices, decay a and gated input b of the
+//                                 recurrence S <- a S + b, all in float32
+//   rglru_scan_kernel             the recurrence over a sequence's tokens, times the other branch
+//   ssd_scan_kernel               S <- exp(A dt) S + dt B x^T,  y = S^T C + D x  per head
+//   gated_group_norm_kernel       (y * silu(z)) normed in equal parts by their own RMS, times w
+//   dual_norm_mean_kernel         (rms(a) wa + rms(b) wb) / 2, written or added to the stream
+//   act_rows_kernel               gelu (tanh form), squared relu, silu on strided columns
+//   residual_add_kernel, gated_rows_add_kernel
+//
+// What a recurrence reads and keeps is float32 whatever the storage type of the projections.
+// A sequence is rows q_start[s] .. q_start[s] + q_len[s] - 1 of the step; its state lives in
+// row seq_slots[s] of a slot-indexed array.  Every sum has an order that depends on the sizes
+// only, so a row's result does not depend on what else is in the step.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace vx {
+
+__device__ __forceinline__ float sq_sigmoid(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float sq_softplus(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float sq_silu(float v) { return v * sq_sigmoid(v); }
+__device__ __forceinline__ float sq_gelu_tanh(float v) {
+  return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+}
+__device__ __forceinline__ float sq_act(float v, int kind) {
+  if (kind == 1) return sq_silu(v);
+  if (kind == 2) return sq_gelu_tanh(v);
+  if (kind == 3) { const float r = fmaxf(v, 0.f); return r * r; }
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void pair_rope_cache_write_kernel(T* __restrict__ qkv, long long stride,
+                                             const int* __restrict__ positions,
+                                             const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                             const int* __restrict__ slots, T* __restrict__ k_cache,
+                                             T* __restrict__ v_cache, int H, int G, int D, int rot, int max_pos,
+                                             long long num_slots, int write_cache, int* status) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;  // 0..H-1 q, H..H+G-1 k, H+G.. v
+  const int half = rot >> 1;
+  const bool is_q = head < H, is_k = !is_q && head < H + G;
+  if (!is_q && !write_cache) return;
+  int pos = positions[t];
+  if (rot > 0 && (pos < 0 || pos >= max_pos)) {
+    if (threadIdx.x == 0 && head == 0) atomicOr(status, VX_STATUS_BAD_POSITION);
+    pos = 0;
+  }
+  const float* c = cos_t + (size_t)pos * half;
+  const float* s = sin_t + (size_t)pos * half;
+  T* row = qkv + (size_t)t * stride + (size_t)head * D;
+  T* dst = row;
+  if (!is_q) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    if ((long long)slot >= num_slots) {
+      if (threadIdx.x == 0) atomicOr(status, VX_STATUS_BAD_SLOT);
+      return;
+    }
+    const int g = is_k ? head - H : head - H - G;
+    dst = (is_k ? k_cache : v_cache) + ((size_t)slot * G + g) * D;
+  }
+  if (is_q || is_k) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+      const float u = to_float(row[2 * i]), v = to_float(row[2 * i + 1]);
+      dst[2 * i] = from_float<T>(u * c[i] - v * s[i]);
+      dst[2 * i + 1] = from_float<T>(v * c[i] + u * s[i]);
+    }
+    if (is_k)
+      for (int i = rot + threadIdx.x; i < D; i += blockDim.x) dst[i] = row[i];
+  } else {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = row[i];
+  }
+}
+
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ logits,
+                                 long long logit_stride, int H, int D) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  for (int idx = threadIdx.x; idx < H * D; idx += blockDim.x) {
+    const int h = idx / D;
+    const float g = sq_sigmoid(to_float(logits[(size_t)t * logit_stride + h]));
+    T* p = out + (size_t)t * out_stride + idx;
+    *p = from_float<T>(to_float(*p) * g);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Convolution.  state[slot][m][c], m = 0 .. taps - 2, is the input at the portion's first
+// position minus (taps - 1 - m); zero before the sequence's start.
+template <typename T>
+__global__ void conv_tokens_kernel(const T* __restrict__ x, long long x_stride, int channels, int taps,
+                                   const float* __restrict__ w, const float* __restrict__ bias,
+                                   const float* __restrict__ state, long long state_stride,
+                                   float* __restrict__ out, long long out_stride,
+                                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ seq_slots, int act) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y;
+  if (c >= channels) return;
+  const int n = q_len[s], start = q_start[s];
+  const float* st = state + (size_t)seq_slots[s] * state_stride;
+  const float b = bias[c];
+  for (int i = blockIdx.z; i < n; i += gridDim.z) {
+    float acc = b;
+    for (int k = 0; k < taps; ++k) {
+      const int j = i - (taps - 1) + k;
+      const float v = j >= 0 ? to_float(x[(size_t)(start + j) * x_stride + c])
+                             : st[(size_t)(taps - 1 + j) * channels + c];
+      acc = fmaf(w[(size_t)c * taps + k], v, acc);
+    }
+    out[(size_t)(start + i) * out_stride + c] = sq_act(acc, act);
+  }
+}
+
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ x, long long x_stride, int channels, int taps,
+                                         float* __restrict__ state, long long state_stride,
+                                         const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                         const int* __restrict__ seq_slots) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y;
+  if (c >= channels) return;
+  const int n = q_len[s], start = q_start[s];
+  if (n <= 0) return;
+  float* st = state + (size_t)seq_slots[s] * state_stride;
+  // Ascending m: what is read lies at or behind what has been written.
+  for (int m = 0; m < taps - 1; ++m) {
+    const int j = n - (taps - 1) + m;
+    const float v = j >= 0 ? to_float(x[(size_t)(start + j) * x_stride + c]) : st[(size_t)(m + n) * channels + c];
+    st[(size_t)m * channels + c] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Gates of the real-gated linear recurrent unit.  u [tokens, width] float32 is cut into `blocks`
+// equal parts; in part b, r = sigmoid(Wa[b] u_b + ba[b]) and i = sigmoid(Wi[b] u_b + bi[b]) with
+// the matrices stored transposed, [blocks][in][out].  a = exp(-c r softplus(lam)),
+// b = sqrt(1 - a^2) i u.
+template <int TT>
+__global__ void rglru_gates_kernel(const float* __restrict__ u, long long u_stride, int part,
+                                   const float* __restrict__ wa_t, const float* __restrict__ ba,
+                                   const float* __restrict__ wi_t, const float* __restrict__ bi,
+                                   const float* __restrict__ lam, float decay_scale, float* __restrict__ a_out,
+                                   float* __restrict__ b_out, long long ab_stride, int num_tokens) {
+  extern __shared__ float u_s[];  // [TT][part]
+  allow_dependents();
+  grid_dependency_wait();
+  const int t0 = blockIdx.x * TT;
+  const int blk = blockIdx.y;
+  for (int idx = threadIdx.x; idx < TT * part; idx += blockDim.x) {
+    const int tt = idx / part, i = idx - tt * part;
+    u_s[idx] = t0 + tt < num_tokens ? u[(size_t)(t0 + tt) * u_stride + (size_t)blk * part + i] : 0.f;
+  }
+  __syncthreads();
+  const float* wa = wa_t + (size_t)blk * part * part;
+  const float* wi = wi_t + (size_t)blk * part * part;
+  for (int o = threadIdx.x; o < part; o += blockDim.x) {
+    float ar[TT], ai[TT];
+    const int c = blk * part + o;
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) { ar[tt] = ba[c]; ai[tt] = bi[c]; }
+    for (int i = 0; i < part; ++i) {
+      const float wr = wa[(size_t)i * part + o], wg = wi[(size_t)i * part + o];
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        const float uv = u_s[tt * part + i];
+        ar[tt] = fmaf(wr, uv, ar[tt]);
+        ai[tt] = fmaf(wg, uv, ai[tt]);
+      }
+    }
+    const float sp = sq_softplus(lam[c]);
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+      if (t0 + tt >= num_tokens) break;
+      const float r = sq_sigmoid(ar[tt]), g = sq_sigmoid(ai[tt]);
+      const float log_a = -decay_scale * r * sp;
+      const float a = expf(log_a);
+      const float mult = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f));
+      a_out[(size_t)(t0 + tt) * ab_stride + c] = a;
+      b_out[(size_t)(t0 + tt) * ab_stride + c] = mult * g * u_s[tt * part + o];
+    }
+  }
+}
+
+// S <- a S + b over a sequence's tokens; out = S * gelu(y).  One thread per (channel, sequence).
+template <typename T>
+__global__ void rglru_scan_kernel(const float* __restrict__ a_in, const float* __restrict__ b_in,
+                                  long long ab_stride, const T* __restrict__ y, long long y_stride, int width,
+                                  float* __restrict__ state, long long state_stride, T* __restrict__ out,
+                                  long long out_stride, const int* __restrict__ q_start,
+                                  const int* __restrict__ q_len, const int* __restrict__ seq_slots, int y_act) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.y;
+  if (c >= width) return;
+  const int n = q_len[s], start = q_start[s];
+  if (n <= 0) return;
+  float* st = state + (size_t)seq_slots[s] * state_stride + c;
+  float S = *st;
+  int i = 0;
+  for (; i + 4 <= n; i += 4) {
+    float a[4], b[4], yv[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const size_t row = (size_t)(start + i + k);
+      a[k] = a_in[row * ab_stride + c];
+      b[k] = b_in[row * ab_stride + c];
+      yv[k] = to_float(y[row * y_stride + c]);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      S = fmaf(a[k], S, b[k]);
+      out[(size_t)(start + i + k) * out_stride + c] = from_float<T>(S * sq_act(yv[k], y_act));
+    }
+  }
+  for (; i < n; ++i) {
+    const size_t row = (size_t)(start + i);
+    S = fmaf(a_in[row * ab_stride + c], S, b_in[row * ab_stride + c]);
+    out[row * out_stride + c] = from_float<T>(S * sq_act(to_float(y[row * y_stride + c]), y_act));
+  }
+  *st = S;
+}
+
+// ---------------------------------------------------------------------------------------------
+// State-space recurrence with a scalar decay per head.  One block per (head, sequence); thread
+// (r, p) keeps SSD_NS state rows n = r * SSD_NS .. of value column p in registers.  Tokens are
+// taken SSD_TC at a time: their B, C, x and dt go to shared memory together.
+constexpr int SSD_NS = 16;
+constexpr int SSD_TC = 8;
+
+template <typename T>
+__global__ void ssd_scan_kernel(const float* __restrict__ xbc, long long xbc_stride, const T* __restrict__ dt_in,
+                                long long dt_stride, const float* __restrict__ dt_bias,
+                                const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                                float* __restrict__ state, long long state_stride, float* __restrict__ y_out,
+                                long long y_stride, int heads, int groups, int N, int P,
+                                const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                const int* __restrict__ seq_slots) {
+  extern __shared__ float ssd_s[];
+  allow_dependents();
+  grid_dependency_wait();
+  const int h = blockIdx.x, s = blockIdx.y;
+  const int n_tok = q_len[s], start = q_start[s];
+  if (n_tok <= 0) return;
+  const int R = (N + SSD_NS - 1) / SSD_NS;
+  const int tid = threadIdx.x;
+  const int r = tid / P, p = tid - r * P;
+  const int g = h / (heads / groups);
+  const int inner = heads * P;
+  float* b_s = ssd_s;                    // [TC][N]
+  float* c_s = b_s + SSD_TC * N;         // [TC][N]
+  float* x_s = c_s + SSD_TC * N;         // [TC][P]
+  float* dt_s = x_s + SSD_TC * P;        // [TC] dt, [TC] decay
+  float* part_s = dt_s + 2 * SSD_TC;     // [TC][R][P]
+  float* st = state + (size_t)seq_slots[s] * state_stride + (size_t)h * N * P;
+  float S[SSD_NS];
+#pragma unroll
+  for (int k = 0; k < SSD_NS; ++k) {
+    const int n = r * SSD_NS + k;
+    S[k] = (r < R && n < N) ? st[(size_t)n * P + p] : 0.f;
+  }
+  const float neg_a = -expf(a_log[h]);
+  const float bias = dt_bias[h], dskip = d_skip[h];
+  for (int i0 = 0; i0 < n_tok; i0 += SSD_TC) {
+    const int tc = min(SSD_TC, n_tok - i0);
+    __syncthreads();
+    for (int idx = tid; idx < tc * N; idx += blockDim.x) {
+      const int k = idx / N, n = idx - k * N;
+      const float* row = xbc + (size_t)(start + i0 + k) * xbc_stride;
+      b_s[k * N + n] = row[inner + g * N + n];
+      c_s[k * N + n] = row[inner + groups * N + g * N + n];
+    }
+    for (int idx = tid; idx < tc * P; idx += blockDim.x) {
+      const int k = idx / P, q = idx - k * P;
+      x_s[k * P + q] = xbc[(size_t)(start + i0 + k) * xbc_stride + (size_t)h * P + q];
+    }
+    if (tid < tc) {
+      const float dt = sq_softplus(to_float(dt_in[(size_t)(start + i0 + tid) * dt_stride + h]) + bias);
+      dt_s[tid] = dt;
+      dt_s[SSD_TC + tid] = expf(neg_a * dt);
+    }
+    __syncthreads();
+    if (r < R) {
+      for (int k = 0; k < tc; ++k) {
+        const float dt = dt_s[k], decay = dt_s[SSD_TC + k];
+        const float xin = dt * x_s[k * P + p];
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < SSD_NS; ++j) {
+          const int n = r * SSD_NS + j;
+          if (n < N) {
+            S[j] = fmaf(decay, S[j], b_s[k * N + n] * xin);
+            acc = fmaf(S[j], c_s[k * N + n], acc);
+          }
+        }
+        part_s[(k * R + r) * P + p] = acc;
+      }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < tc * P; idx += blockDim.x) {
+      const int k = idx / P, q = idx - k * P;
+      float acc = 0.f;
+      for (int rr = 0; rr < R; ++rr) acc += part_s[(k * R + rr) * P + q];
+      y_out[(size_t)(start + i0 + k) * y_stride + (size_t)h * P + q] = acc + dskip * x_s[k * P + q];
+    }
+  }
+  if (r < R) {
+#pragma unroll
+    for (int k = 0; k < SSD_NS; ++k) {
+      const int n = r * SSD_NS + k;
+      if (n < N) st[(size_t)n * P + p] = S[k];
+    }
+  }
+}
+
+// out[t, part] = (y * silu(z)) / rms over the part * w, parts of equal size.
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, long long y_stride, const T* __restrict__ z,
+                                        long long z_stride, const float* __restrict__ w, float eps, int part,
+                                        T* __restrict__ out, long long out_stride) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x, gidx = blockIdx.y;
+  const size_t off = (size_t)gidx * part;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < part; i += blockDim.x) {
+    const float v = y[(size_t)t * y_stride + off + i] * sq_silu(to_float(z[(size_t)t * z_stride + off + i]));
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf(block_sum(ss, scratch) / (float)part + eps);
+  for (int i = threadIdx.x; i < part; i += blockDim.x) {
+    const float v = y[(size_t)t * y_stride + off + i] * sq_silu(to_float(z[(size_t)t * z_stride + off + i]));
+    out[(size_t)t * out_stride + off + i] = from_float<T>(v * inv * w[off + i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// value = scale * (a / rms(a) * wa + b / rms(b) * wb); resid += value when resid is given, else
+// out = value.
+template <typename T>
+__global__ void dual_norm_mean_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ wa,
+                                      const float* __restrict__ wb, float eps, float scale, int width,
+                                      float* __restrict__ resid, T* __restrict__ out) {
+  __shared__ float scratch[32];
+  allow_dependents();
+  grid_dependency_wait();
+  const size_t base = (size_t)blockIdx.x * width;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float va = to_float(a[base + i]), vb = to_float(b[base + i]);
+    sa = fmaf(va, va, sa);
+    sb = fmaf(vb, vb, sb);
+  }
+  const float ia = rsqrtf(block_sum(sa, scratch) / (float)width + eps);
+  const float ib = rsqrtf(block_sum(sb, scratch) / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = scale * (to_float(a[base + i]) * ia * wa[i] + to_float(b[base + i]) * ib * wb[i]);
+    if (resid != nullptr) resid[base + i] += v;
+    else out[base + i] = from_float<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void act_rows_kernel(const T* __restrict__ x, long long x_stride, T* __restrict__ out,
+                                long long out_stride, int width, long long total, int kind) {
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / width;
+    const int i = (int)(idx - t * width);
+    out[t * out_stride + i] = from_float<T>(sq_act(to_float(x[t * x_stride + i]), kind));
+  }
+}
+
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ resid, const T* __restrict__ delta, long long total) {
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x)
+    resid[idx] += to_float(delta[idx]);
+}
+
+// resid[t, :] += sigmoid(logit[t]) * x[t, :]
+template <typename T>
+__global__ void gated_rows_add_kernel(float* __restrict__ resid, const T* __restrict__ x, const T* __restrict__ logit,
+                                      long long logit_stride, int width, long long total) {
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / width;
+    resid[idx] += sq_sigmoid(to_float(logit[t * logit_stride])) * to_float(x[idx]);
+  }
+}
+
+}  // namespace vx
+
+using namespace vx;
+
+#define VX_BY_DTYPE(dtype, CALL)                      \
+  if ((dtype) == VX_DTYPE_F32) { using T = float; CALL; } \
+  else { using T = __nv_bfloat16; CALL; }
+
+static inline int grid_for(long long total, int block) {
+  long long blocks = (total + block - 1) / block;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return blocks < 1 ? 1 : (int)blocks;
+}
+
+VX_API int vx_pair_rope_cache_write(void* qkv, int dtype, long long stride, const int* positions, const float* cos_t,
+                                    const float* sin_t, const int* slots, void* k_cache, void* v_cache,
+                                    int num_tokens, int H, int G, int D, int rot, int max_pos, long long num_slots,
+                                    int write_cache, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const dim3 grid(num_tokens, H + 2 * G);
+  const int threads = D >= 128 ? 64 : 32;
+  VX_BY_DTYPE(dtype, launch_pdl(pair_rope_cache_write_kernel<T>, grid, dim3(threads), 0, stream, (T*)qkv, stride,
+                                positions, cos_t, sin_t, slots, (T*)k_cache, (T*)v_cache, H, G, D, rot, max_pos,
+                                num_slots, write_cache, status));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_head_gate(void* out, int dtype, long long out_stride, const void* logits, long long logit_stride,
+                        int num_tokens, int H, int D, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int work = H * D;
+  const int threads = work >= 256 ? 256 : (work + 31) / 32 * 32;
+  VX_BY_DTYPE(dtype, launch_pdl(head_gate_kernel<T>, dim3(num_tokens), dim3(threads), 0, stream, (T*)out,
+                                out_stride, (const T*)logits, logit_stride, H, D));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_conv_tokens(const void* x, int dtype, long long x_stride, int channels, int taps, const float* w,
+                          const float* bias, float* state, long long state_stride, float* out,
+                          long long out_stride, const int* q_start, const int* q_len, const int* seq_slots,
+                          int num_seqs, int token_lanes, int act, cudaStream_t stream) {
+  if (num_seqs <= 0 || channels <= 0) return 0;
+  if (token_lanes < 1) token_lanes = 1;
+  if (token_lanes > 64) token_lanes = 64;
+  const dim3 grid((channels + 127) / 128, num_seqs, token_lanes);
+  VX_BY_DTYPE(dtype, launch_pdl(conv_tokens_kernel<T>, grid, dim3(128), 0, stream, (const T*)x, x_stride, channels,
+                                taps, w, bias, (const float*)state, state_stride, out, out_stride, q_start, q_len,
+                                seq_slots, act));
+  int e = (int)cudaGetLastError();
+  if (e != 0) return e;
+  const dim3 grid2((channels + 127) / 128, num_seqs);
+  VX_BY_DTYPE(dtype, launch_pdl(conv_state_update_kernel<T>, grid2, dim3(128), 0, stream, (const T*)x, x_stride,
+                                channels, taps, state, state_stride, q_start, q_len, seq_slots));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_rglru_gates(const float* u, long long u_stride, int width, int blocks, const float* wa_t,
+                          const float* ba, const float* wi_t, const float* bi, const float* lam, float decay_scale,
+                          float* a_out, float* b_out, long long ab_stride, int num_tokens, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int part = width / blocks;
+  const int threads = part >= 256 ? 256 : (part + 31) / 32 * 32;
+  if (num_tokens <= 8) {
+    constexpr int TT = 2;
+    const size_t smem = sizeof(float) * TT * part;
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    launch_pdl(rglru_gates_kernel<TT>, dim3((num_tokens + TT - 1) / TT, blocks), dim3(threads), smem, stream, u,
+               u_stride, part, wa_t, ba, wi_t, bi, lam, decay_scale, a_out, b_out, ab_stride, num_tokens);
+  } else {
+    constexpr int TT = 16;
+    const size_t smem = sizeof(float) * TT * part;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+      cudaError_t e = cudaFuncSetAttribute(rglru_gates_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = smem;
+    }
+    launch_pdl(rglru_gates_kernel<TT>, dim3((num_tokens + TT - 1) / TT, blocks), dim3(threads), smem, stream, u,
+               u_stride, part, wa_t, ba, wi_t, bi, lam, decay_scale, a_out, b_out, ab_stride, num_tokens);
+  }
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_rglru_scan(const float* a_in, const float* b_in, long long ab_stride, const void* y, int dtype,
+                         long long y_stride, int width, float* state, long long state_stride, void* out,
+                         long long out_stride, const int* q_start, const int* q_len, const int* seq_slots,
+                         int num_seqs, int y_act, cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  const dim3 grid((width + 63) / 64, num_seqs);
+  VX_BY_DTYPE(dtype, launch_pdl(rglru_scan_kernel<T>, grid, dim3(64), 0, stream, a_in, b_in, ab_stride,
+                                (const T*)y, y_stride, width, state, state_stride, (T*)out, out_stride, q_start,
+                                q_len, seq_slots, y_act));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_ssd_scan(const float* xbc, long long xbc_stride, const void* dt_in, int dtype, long long dt_stride,
+                       const float* dt_bias, const float* a_log, const float* d_skip, float* state,
+                       long long state_stride, float* y_out, long long y_stride, int heads, int groups, int N,
+                       int P, const int* q_start, const int* q_len, const int* seq_slots, int num_seqs,
+                       cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  const int R = (N + SSD_NS - 1) / SSD_NS;
+  const int threads = (R * P + 31) / 32 * 32;
+  if (threads > 1024 || threads < SSD_TC) return (int)cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * ((size_t)2 * SSD_TC * N + (size_t)SSD_TC * P + 2 * SSD_TC +
+                                       (size_t)SSD_TC * R * P);
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  VX_BY_DTYPE(dtype, launch_pdl(ssd_scan_kernel<T>, dim3(heads, num_seqs), dim3(threads), smem, stream, xbc,
+                                xbc_stride, (const T*)dt_in, dt_stride, dt_bias, a_log, d_skip, state, state_stride,
+                                y_out, y_stride, heads, groups, N, P, q_start, q_len, seq_slots));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_gated_group_norm(const float* y, long long y_stride, const void* z, int dtype, long long z_stride,
+                               const float* w, float eps, int inner, int parts, void* out, long long out_stride,
+                               int num_tokens, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int part = inner / parts;
+  const int threads = part >= 256 ? 256 : (part + 31) / 32 * 32;
+  VX_BY_DTYPE(dtype, launch_pdl(gated_group_norm_kernel<T>, dim3(num_tokens, parts), dim3(threads), 0, stream, y,
+                                y_stride, (const T*)z, z_stride, w, eps, part, (T*)out, out_stride));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_dual_norm_mean(const void* a, const void* b, int dtype, const float* wa, const float* wb, float eps,
+                             float scale, int width, float* resid, void* out, int num_tokens,
+                             cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  VX_BY_DTYPE(dtype, launch_pdl(dual_norm_mean_kernel<T>, dim3(num_tokens), dim3(threads), 0, stream, (const T*)a,
+                                (const T*)b, wa, wb, eps, scale, width, resid, (T*)out));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_act_rows(const void* x, int dtype, long long x_stride, void* out, long long out_stride, int width,
+                       int num_tokens, int kind, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const long long total = (long long)num_tokens * width;
+  VX_BY_DTYPE(dtype, launch_pdl(act_rows_kernel<T>, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const T*)x,
+                                x_stride, (T*)out, out_stride, width, total, kind));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_residual_add(float* resid, const void* delta, int dtype, long long total, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  VX_BY_DTYPE(dtype, launch_pdl(residual_add_kernel<T>, dim3(grid_for(total, 256)), dim3(256), 0, stream, resid,
+                                (const T*)delta, total));
+  return (int)cudaGetLastError();
+}
+
+VX_API int vx_gated_rows_add(float* resid, const void* x, const void* logit, int dtype, long long logit_stride,
+                             int width, int num_tokens, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const long long total = (long long)num_tokens * width;
+  VX_BY_DTYPE(dtype, launch_pdl(gated_rows_add_kernel<T>, dim3(grid_for(total, 256)), dim3(256), 0, stream, resid,
+                                (const T*)x, (const T*)logit, logit_stride, width, total));
+  return (int)cudaGetLastError();
+}

@@ -78,7 +78,7 @@ class CausalLM:
         self.cache_groups: List[CacheGroup] = []
         self.entry_needs: List[CacheNeeds] = []
         self.entry_group: List[Optional[int]] = []
-        by_window: Dict[Optional[int], int] = {}
+        by_window: Dict[tuple, int] = {}
         for entry in spec.schedule:
             needs = self.blocks[entry.layer].mixer.cache_needs()
             self.entry_needs.append(needs)
@@ -86,11 +86,12 @@ class CausalLM:
                 self.entry_group.append(None)
                 continue
             window = needs.paged.window
-            if window not in by_window:
-                by_window[window] = len(self.cache_groups)
-                name = "all_keys" if window is None else f"window_{window}"
-                self.cache_groups.append(CacheGroup(name=name, window=window))
-            self.entry_group.append(by_window[window])
+            keep_first = needs.paged.keep_first if window is not None else 0
+            if (window, keep_first) not in by_window:
+                by_window[(window, keep_first)] = len(self.cache_groups)
+                name = "all_keys" if window is None else f"window_{window}" + (f"_keep_{keep_first}" if keep_first else "")
+                self.cache_groups.append(CacheGroup(name=name, window=window, keep_first=keep_first))
+            self.entry_group.append(by_window[(window, keep_first)])
         if not self.cache_groups:
             # A model without paged state still gets one (empty) group so tables exist.
             self.cache_groups.append(CacheGroup(name="all_keys", window=None))
@@ -139,6 +140,8 @@ class CausalLM:
         resid = home(ws) if home is not None else None
         if resid is None:
             resid = ws.get("model.resid", (ws.max_tokens, self.hidden_size), torch.float32)
+        # Parts that look something up by token id (a table of experts) find the ids here.
+        ctx.token_ids = input_ids
         self.embedding.forward(input_ids, resid, ctx)
         hidden = HiddenState(resid=resid, delta=None)
         for index, entry in enumerate(self.spec.schedule):

@@ -123,6 +123,8 @@ class StepContext:
     # Set by a block around a part's call when it can take the part's product as float32 sums
     # (``parts.base.PendingSums``) instead of rows in the compute dtype.
     takes_pending_sums: bool = False
+    # The step's token ids on the device (int32; -1 - r stands for row r of ``fed_tokens``).
+    token_ids: Optional[torch.Tensor] = None
     # Host copies, for parts that lay out work of their own.
     q_lens_host: List[int] = field(default_factory=list)
     kv_lens_host: List[int] = field(default_factory=list)
@@ -244,7 +246,7 @@ class ModelRunner:
         # Not a planner option: up to how many keys the layout without splits through memory is
         # used for padded single-token steps (tests move it down to their sizes).
         self.short_reach = int(self.plan_overrides.pop("short_reach", self.SHORT_REACH))
-        if [g.window for g in cache.groups] != [g.window for g in model.cache_groups]:
+        if [(g.window, g.keep_first) for g in cache.groups] != [(g.window, g.keep_first) for g in model.cache_groups]:
             raise ValueError("the cache manager's groups are not the model's cache groups")
 
         self.workspace = Workspace(self.max_tokens, max_logit_rows or max_num_seqs, self.device)
@@ -603,7 +605,8 @@ class ModelRunner:
                 device_plan.num_merges = shape[0]
                 device_plan.merge_rows = max(ap.TILE_ROWS[kind] for kind in entry)
                 needed = shape[0] * key[1][0]
-                if self.dtype != torch.float32 and needed <= self._split_counters.numel():
+                if (self.dtype != torch.float32 and needed <= self._split_counters.numel()
+                        and not (len(key[1]) > 5 and key[1][5])):
                     device_plan.split_counters = self._split_counters
             if plan.partial_rows:
                 head_dim = key[1][3]
@@ -636,7 +639,7 @@ class ModelRunner:
     def _plan_options(self, signature) -> "ap.PlanOptions":
         """How attention work is cut for layers of this (KV heads, heads per KV head, window,
         head size): what an SM holds of the kernels depends on the head size."""
-        num_kv_heads, heads_per_kv, window, head_dim = signature
+        num_kv_heads, heads_per_kv, window, head_dim = signature[:4]
         use_f32 = self.dtype == torch.float32
         options = dict(num_kv_heads=num_kv_heads, group=heads_per_kv, window=window, use_f32=use_f32,
                        target_ctas=2 * self.num_sms)
@@ -648,6 +651,11 @@ class ModelRunner:
         if "target_ctas" in self.plan_overrides and "narrow_target_ctas" not in self.plan_overrides:
             options["narrow_target_ctas"] = self.plan_overrides["target_ctas"]
         options.update(self.plan_overrides)
+        if len(signature) > 4:
+            # (..., keep_first, anchored): the first keys a window keeps, and whether the rows are
+            # finished by the merge kernel (a sink in the denominator, kept first keys).
+            options["keep_first"] = int(signature[4] or 0)
+            options["anchored"] = bool(signature[5])
         return ap.PlanOptions(**options)
 
     # Key tiles per work item from which the tensor-memory attention runs two CTAs on an SM when
@@ -671,6 +679,8 @@ class ModelRunner:
         """(splits through memory, cluster size) of a padded single-token step: enough CTAs to
         fill the GPU at this batch size, the same for every sequence of up to ``reach`` keys
         (``max_model_len`` if not given) whatever its length."""
+        if opt.anchored:
+            return 2, 1
         tiles = -(-opt.group // 16)
         per_split = max(1, num_seqs * opt.num_kv_heads * tiles)
         narrow = not opt.use_f32 and opt.group <= opt.narrow_max_rows

@@ -1,2 +1,2 @@
 """Built-in architectures.  Importing this package registers them."""
-from . import peratar, qwen2  # noqa: F401
+from . import peratar, qwen2, redalix  # noqa: F401

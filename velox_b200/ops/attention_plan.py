@@ -75,6 +75,12 @@ class PlanOptions:
     # as few as ``narrow_global_fine_keys``.
     narrow_global_split_keys: int = 1024
     narrow_global_fine_keys: int = 512
+    # With a window: keys 0 .. keep_first - 1 stay visible behind it.
+    keep_first: int = 0
+    # Every tile's result goes through partial rows and the merge kernel, which is where a sink
+    # joins the softmax denominator and where the kept first keys (a key range of their own,
+    # before the window's) meet the window's keys: see ``plan_anchored``.
+    anchored: bool = False
 
 
 def splits_through_memory(span, cluster: int, opt: PlanOptions):
@@ -157,6 +163,8 @@ def plan_attention(
     Without forced splits the layout of a long step is computed with arrays
     (``_plan_with_arrays``); the loops of ``plan_attention_plain`` say the same thing tile by
     tile, serve the short steps, and are what the tests compare the arrays with."""
+    if opt.anchored:
+        return plan_anchored(q_lens, kv_lens, opt, always_two=fixed_splits is not None)
     if fixed_splits is None:
         # The arrays cost about as much as forty tiles of the loops, whatever the step.
         rows = sum(q_lens) * opt.group
@@ -378,6 +386,57 @@ def plan_attention_plain(
     return plan
 
 
+def _kind_of(rows: int, opt: PlanOptions) -> int:
+    if opt.use_f32:
+        return KIND_F32
+    if rows <= opt.narrow_max_rows:
+        return KIND_BF16_NARROW
+    return KIND_BF16_TC if opt.wide_on_tensor_memory else KIND_BF16_WIDE
+
+
+def plan_anchored(q_lens: Sequence[int], kv_lens: Sequence[int], opt: PlanOptions,
+                  always_two: bool = False) -> AttentionPlan:
+    """The layout of layers whose rows are finished by the merge kernel (``opt.anchored``).
+
+    Every tile of rows gets one work item over the keys its window reaches, ``[lo, hi)``, and,
+    where the window has left kept first keys behind (``keep_first > 0`` and ``lo > 0``), a second
+    one over ``[0, min(keep_first, lo))``; the kernels' visibility test lets a row see a key
+    inside its window or below ``keep_first``, so both ranges are masked row by row as usual.
+    Both write partial rows and their log-sum-exps; one merge item per tile names them, and the
+    merge kernel weights them and adds the sink.  No key range is cut further and no cluster
+    shares an item: a window bounds what a tile reads.  ``always_two`` gives every tile both
+    items (the second possibly empty), so that the layout's shape depends on the batch alone."""
+    per_kind: Dict[int, List[List[int]]] = {}
+    merges: List[List[int]] = []
+    partial_rows = 0
+    for seq, (q_len, kv_len) in enumerate(zip(q_lens, kv_lens)):
+        rows = q_len * opt.group
+        if rows <= 0:
+            continue
+        kind = _kind_of(rows, opt)
+        height = TILE_ROWS[kind]
+        out = per_kind.setdefault(kind, [])
+        for row_begin in range(0, rows, height):
+            row_count = min(height, rows - row_begin)
+            lo, hi = _key_range(q_len, kv_len, opt.group, opt.window, row_begin, row_count)
+            kept = min(max(opt.keep_first, 0), lo)
+            count = 2 if (kept > 0 or always_two) else 1
+            stride = opt.num_kv_heads * row_count
+            merge_index = len(merges)
+            merges.append([seq, row_begin, row_count, partial_rows, count, stride, 0, 0])
+            out.append([seq, row_begin, row_count, lo, hi, partial_rows, merge_index, count])
+            partial_rows += stride
+            if count == 2:
+                out.append([seq, row_begin, row_count, 0, kept, partial_rows, merge_index, count])
+                partial_rows += stride
+    plan = AttentionPlan(partial_rows=partial_rows, cluster=1)
+    for kind, rows_ in per_kind.items():
+        plan.items[kind] = np.asarray(rows_, dtype=np.int32).reshape(-1, ITEM_WIDTH)
+    if merges:
+        plan.merge_items = np.asarray(merges, dtype=np.int32).reshape(-1, ITEM_WIDTH)
+    return plan
+
+
 def round_plan(plan: AttentionPlan, round_count) -> AttentionPlan:
     """The same work with every array padded to ``round_count(length)`` entries: padding work
     items and merge items have sequence -1 and do nothing.  Plans of steps that differ a little
@@ -437,6 +496,9 @@ def plan_single_tokens(kv_lens: np.ndarray, num_seqs: int, splits: int, opt: Pla
         raise ValueError("plan_single_tokens handles one 16-row tile per sequence")
     kind = KIND_F32 if opt.use_f32 else KIND_BF16_NARROW
     n = len(kv_lens)
+    if opt.anchored:
+        plan = pad_plan(plan_anchored([1] * n, [int(v) for v in kv_lens], opt, always_two=True), num_seqs, 2, opt)
+        return kind, plan.items[kind], plan.merge_items, plan.partial_rows
     splits = max(splits, 1)
     items = np.zeros((num_seqs * splits, ITEM_WIDTH), np.int32)
     items[:, 0] = -1

@@ -106,13 +106,56 @@ def core():
     return _core
 
 
+_mixers = None
+
+
+def mixers():
+    """The library of recurrent mixers and expert feed-forwards (built at first use)."""
+    global _mixers
+    if _mixers is None:
+        lib = build.load_mixers()
+        lib.vx_pair_rope_cache_write.argtypes = [
+            _ptr, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+            _c_ll, _c_int, _ptr, _ptr,
+        ]
+        lib.vx_head_gate.argtypes = [_ptr, _c_int, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr]
+        lib.vx_conv_tokens.argtypes = [
+            _ptr, _c_int, _c_ll, _c_int, _c_int, _ptr, _ptr, _ptr, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _c_int,
+            _c_int, _c_int, _ptr,
+        ]
+        lib.vx_rglru_gates.argtypes = [
+            _ptr, _c_ll, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_f, _ptr, _ptr, _c_ll, _c_int, _ptr,
+        ]
+        lib.vx_rglru_scan.argtypes = [
+            _ptr, _ptr, _c_ll, _ptr, _c_int, _c_ll, _c_int, _ptr, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _c_int,
+            _c_int, _ptr,
+        ]
+        lib.vx_ssd_scan.argtypes = [
+            _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int,
+            _c_int, _ptr, _ptr, _ptr, _c_int, _ptr,
+        ]
+        lib.vx_gated_group_norm.argtypes = [
+            _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _c_f, _c_int, _c_int, _ptr, _c_ll, _c_int, _ptr,
+        ]
+        lib.vx_dual_norm_mean.argtypes = [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _c_f, _c_int, _ptr, _ptr, _c_int, _ptr]
+        lib.vx_act_rows.argtypes = [_ptr, _c_int, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int, _ptr]
+        lib.vx_residual_add.argtypes = [_ptr, _ptr, _c_int, _c_ll, _ptr]
+        lib.vx_gated_rows_add.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_ll, _c_int, _c_int, _ptr]
+        lib.vx_table_experts.argtypes = [
+            _ptr, _c_int, _c_ll, _ptr, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _ptr,
+            _c_int, _ptr, _ptr,
+        ]
+        _mixers = lib
+    return _mixers
+
+
 def attention_lib(head_dim: int):
     lib = _attention.get(head_dim)
     if lib is None:
         lib = build.load_attention(head_dim)
         lib.vx_attention.argtypes = [
             _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr,
-            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _c_int, _ptr,
+            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_int, _c_f, _c_int, _c_int, _ptr,
         ]
         lib.vx_attn_has_tc.restype = _c_int
         lib.vx_attn_narrow_ctas_per_sm.restype = _c_int
@@ -120,7 +163,7 @@ def attention_lib(head_dim: int):
         lib.vx_attn_narrow_max_active_clusters.restype = _c_int
         lib.vx_attn_narrow_max_active_clusters.argtypes = [_c_int]
         lib.vx_attention_merge.argtypes = [
-            _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr,
+            _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr,
         ]
         lib.vx_attn_head_dim.restype = _c_int
         if lib.vx_attn_head_dim() != head_dim:
@@ -927,6 +970,7 @@ def attention(
     status: Optional[torch.Tensor] = None,
     cluster: int = 1,
     layout_checked: bool = False,
+    keep_first: int = 0,
 ) -> None:
     """Run ``num_items`` work items (see attention.cu for their layout) of one kernel family.
 
@@ -938,7 +982,8 @@ def attention(
     ``cluster`` (1, 2, 4 or 8; narrow bfloat16 family) CTAs share every item as a thread-block
     cluster: each takes a run of the item's key tiles and they merge through distributed shared
     memory.  For the tensor-memory family 2 asks for two CTAs on an SM whatever the grid's size
-    (the caller knows that the items' key ranges are long).
+    (the caller knows that the items' key ranges are long).  ``keep_first`` (with a window): keys
+    0 .. keep_first - 1 stay visible to every later query.
     """
     want = torch.float32 if kind == ATTN_F32 else torch.bfloat16
     _need(q, want, "q")
@@ -968,7 +1013,7 @@ def attention(
                          q.shape[1], out.shape[1],
                          block_tables.shape[1], num_kv_heads, num_heads // num_kv_heads,
                          k_cache.shape[1], k_cache.shape[0], int(window or 0), float(softmax_scale),
-                         int(cluster), _stream()),
+                         int(cluster), int(keep_first or 0), _stream()),
         "attention",
     )
 
@@ -1024,14 +1069,21 @@ def attention_merge(
     num_kv_heads: int,
     head_dim: int,
     max_rows: int = 64,
+    sinks: Optional[torch.Tensor] = None,
 ) -> None:
-    """Combine the splits of the merge items; ``max_rows`` bounds the rows of any item."""
+    """Combine the splits of the merge items; ``max_rows`` bounds the rows of any item.
+    ``sinks`` (float32, one per query head): exp(sink) joins every row's softmax denominator,
+    with no key and no value."""
     _need(merge_items, torch.int32, "merge_items")
+    if sinks is not None:
+        _need(sinks, torch.float32, "sinks")
+        if sinks.numel() != num_heads:
+            raise ValueError("one sink per query head is needed")
     lib = attention_lib(head_dim)
     _check(
         lib.vx_attention_merge(_code(out.dtype), _p(out), _p(q_start), _p(merge_items), num_items,
                                max_rows, _p(partial_o), _p(partial_lse), out.shape[1], num_kv_heads,
-                               num_heads // num_kv_heads, _stream()),
+                               num_heads // num_kv_heads, _p(sinks), _stream()),
         "attention_merge",
     )
 
@@ -1142,4 +1194,184 @@ def apply_penalties(
                                   _p(counts), _p(repetition), _p(presence), _p(frequency),
                                   _stream()),
         "apply_penalties",
+    )
+
+
+# ------------------------------------------------------------------------------------------
+# Recurrent mixers, expert feed-forwards and the row-wise kernels around them (csrc/sequence.cu,
+# csrc/routed.cu).  Tensors may be column ranges of wider buffers: a row pitch is passed.
+ACT_NONE, ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2, 3
+
+
+def _pitched(t: torch.Tensor, name: str) -> int:
+    """Row pitch (elements) of a 2-D tensor whose rows are contiguous."""
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError(f"{name} must be 2-D with contiguous rows")
+    return t.stride(0)
+
+
+def pair_rope_cache_write(qkv, positions, cos, sin, slots, k_cache, v_cache, num_tokens, num_heads, num_kv_heads,
+                          head_dim, rotary_dim, status) -> None:
+    """Neighbouring pairs (2i, 2i + 1) of the first ``rotary_dim`` dims of every q and k head turn
+    by the tabulated angles (q in place); k and v go to the cache at ``slots``.  The rows of
+    ``qkv`` hold q | k | v and possibly further columns behind them."""
+    stride = _pitched(qkv, "qkv")
+    if qkv.shape[1] < (num_heads + 2 * num_kv_heads) * head_dim:
+        raise ValueError("qkv rows are narrower than the heads")
+    write = k_cache is not None
+    if write:
+        _need(k_cache, qkv.dtype, "k_cache")
+        _need(v_cache, qkv.dtype, "v_cache")
+    if rotary_dim > 0:
+        _need(cos, torch.float32, "cos")
+        _need(sin, torch.float32, "sin")
+        if cos.shape[1] != rotary_dim // 2 or rotary_dim % 2 or rotary_dim > head_dim:
+            raise ValueError("cos/sin tables do not match the rotary width")
+    _check(
+        mixers().vx_pair_rope_cache_write(
+            _p(qkv), _code(qkv.dtype), stride, _p(positions), _p(cos) if rotary_dim > 0 else None,
+            _p(sin) if rotary_dim > 0 else None, _p(slots), _p(k_cache), _p(v_cache), num_tokens, num_heads,
+            num_kv_heads, head_dim, rotary_dim, cos.shape[0] if rotary_dim > 0 else 0,
+            k_cache.shape[0] * k_cache.shape[1] if write else 0, 1 if write else 0, _p(status), _stream()),
+        "pair_rope_cache_write",
+    )
+
+
+def head_gate(out, logits, num_tokens, num_heads, head_dim) -> None:
+    """out[t, h, :] *= sigmoid(logits[t, h])."""
+    _check(mixers().vx_head_gate(_p(out), _code(out.dtype), _pitched(out, "out"), _p(logits),
+                                 _pitched(logits, "logits"), num_tokens, num_heads, head_dim, _stream()),
+           "head_gate")
+
+
+def conv_tokens(x, weight, bias, state, out, q_start, q_len, seq_slots, num_seqs, num_tokens, act) -> None:
+    """Causal convolution per channel over each sequence's tokens and the update of its state.
+
+    ``x`` [tokens, channels] (a column range is fine), ``weight`` float32 [channels, taps] with
+    the last column the current token's, ``state`` float32 [slots, (taps - 1) * channels]: the
+    last taps - 1 inputs of each slot's sequence.  ``out`` float32 [tokens, channels]."""
+    _need(weight, torch.float32, "conv weight")
+    _need(bias, torch.float32, "conv bias")
+    channels, taps = weight.shape
+    if x.shape[1] != channels or out.shape[1] != channels or out.dtype != torch.float32:
+        raise ValueError("conv_tokens: widths do not agree")
+    if state.dtype != torch.float32 or state.shape[1] < (taps - 1) * channels:
+        raise ValueError("conv_tokens: the state is too small")
+    _check(
+        mixers().vx_conv_tokens(_p(x), _code(x.dtype), _pitched(x, "x"), channels, taps, _p(weight), _p(bias),
+                                _p(state), _pitched(state, "state"), _p(out), _pitched(out, "out"), _p(q_start),
+                                _p(q_len), _p(seq_slots), num_seqs, max(1, min(64, num_tokens)), act, _stream()),
+        "conv_tokens",
+    )
+
+
+def rglru_gates(u, w_a_t, b_a, w_i_t, b_i, lam, decay_scale, a_out, b_out, num_tokens) -> None:
+    """Decay and gated input of S <- a S + b from u float32 [tokens, width]; the gate matrices are
+    block-diagonal, stored transposed [blocks, in, out], all float32."""
+    blocks, part, _ = w_a_t.shape
+    for name, t in (("w_a_t", w_a_t), ("b_a", b_a), ("w_i_t", w_i_t), ("b_i", b_i), ("lam", lam)):
+        _need(t, torch.float32, name)
+    _check(
+        mixers().vx_rglru_gates(_p(u), _pitched(u, "u"), blocks * part, blocks, _p(w_a_t), _p(b_a), _p(w_i_t),
+                                _p(b_i), _p(lam), float(decay_scale), _p(a_out), _p(b_out), _pitched(a_out, "a_out"),
+                                num_tokens, _stream()),
+        "rglru_gates",
+    )
+
+
+def rglru_scan(a_in, b_in, y, state, out, q_start, q_len, seq_slots, num_seqs, y_act) -> None:
+    """S <- a S + b over every sequence's tokens from the state of its slot (float32
+    [slots, width]); out = S * act(y)."""
+    width = a_in.shape[1]
+    _check(
+        mixers().vx_rglru_scan(_p(a_in), _p(b_in), _pitched(a_in, "a_in"), _p(y), _code(y.dtype), _pitched(y, "y"),
+                               width, _p(state), _pitched(state, "state"), _p(out), _pitched(out, "out"),
+                               _p(q_start), _p(q_len), _p(seq_slots), num_seqs, y_act, _stream()),
+        "rglru_scan",
+    )
+
+
+def ssd_scan(xbc, dt, dt_bias, a_log, d_skip, state, y_out, heads, groups, state_size, value_dim, q_start, q_len,
+             seq_slots, num_seqs) -> None:
+    """Per head: S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + D x with dt = softplus(dt +
+    dt_bias); ``xbc`` float32 rows hold x | B | C, ``state`` float32 [slots, heads * N * P]."""
+    _check(
+        mixers().vx_ssd_scan(_p(xbc), _pitched(xbc, "xbc"), _p(dt), _code(dt.dtype), _pitched(dt, "dt"),
+                             _p(dt_bias), _p(a_log), _p(d_skip), _p(state), _pitched(state, "state"), _p(y_out),
+                             _pitched(y_out, "y_out"), heads, groups, state_size, value_dim, _p(q_start), _p(q_len),
+                             _p(seq_slots), num_seqs, _stream()),
+        "ssd_scan",
+    )
+
+
+def gated_group_norm(y, z, weight, eps, parts, out, num_tokens) -> None:
+    """out = (y * silu(z)) divided, in ``parts`` equal parts, by each part's RMS, times weight."""
+    inner = weight.numel()
+    _check(
+        mixers().vx_gated_group_norm(_p(y), _pitched(y, "y"), _p(z), _code(z.dtype), _pitched(z, "z"), _p(weight),
+                                     float(eps), inner, parts, _p(out), _pitched(out, "out"), num_tokens, _stream()),
+        "gated_group_norm",
+    )
+
+
+def dual_norm_mean(a, b, w_a, w_b, eps, scale, num_tokens, resid=None, out=None) -> None:
+    """scale * (rms_norm(a) * w_a + rms_norm(b) * w_b): added to ``resid`` (float32) or written
+    to ``out``."""
+    _need(a, a.dtype, "a")
+    _need(b, a.dtype, "b")
+    if (resid is None) == (out is None):
+        raise ValueError("dual_norm_mean writes either into the stream or to a buffer")
+    _check(
+        mixers().vx_dual_norm_mean(_p(a), _p(b), _code(a.dtype), _p(w_a), _p(w_b), float(eps), float(scale),
+                                   a.shape[1], _p(resid), _p(out), num_tokens, _stream()),
+        "dual_norm_mean",
+    )
+
+
+def act_rows(x, out, num_tokens, kind) -> None:
+    """out = act(x) column by column; both may be column ranges of wider buffers."""
+    _check(
+        mixers().vx_act_rows(_p(x), _code(x.dtype), _pitched(x, "x"), _p(out), _pitched(out, "out"), out.shape[1],
+                             num_tokens, kind, _stream()),
+        "act_rows",
+    )
+
+
+def residual_add(resid, delta, num_tokens) -> None:
+    """resid[:n] += delta[:n] in float32."""
+    _need(resid, torch.float32, "resid")
+    _need(delta, delta.dtype, "delta")
+    _check(mixers().vx_residual_add(_p(resid), _p(delta), _code(delta.dtype), num_tokens * resid.shape[1], _stream()),
+           "residual_add")
+
+
+def gated_rows_add(resid, x, logit, num_tokens) -> None:
+    """resid[t, :] += sigmoid(logit[t]) * x[t, :]; ``logit`` is one column of a wider buffer."""
+    _need(resid, torch.float32, "resid")
+    _need(x, x.dtype, "x")
+    _check(
+        mixers().vx_gated_rows_add(_p(resid), _p(x), _p(logit), _code(x.dtype), _pitched(logit, "logit"),
+                                   resid.shape[1], num_tokens, _stream()),
+        "gated_rows_add",
+    )
+
+
+def table_experts(h, ids, fed, table, w_up, w_down, resid, num_tokens, status) -> None:
+    """Every token's experts, named by row ``ids[t]`` of ``table`` [vocab, top]: the mean of
+    ``W_down[e] relu(W_up[e] h)^2`` over them is added to ``resid``.  ``w_up`` [experts, ff,
+    width], ``w_down`` [experts, width, ff]."""
+    _need(table, torch.int32, "table")
+    _need(ids, torch.int32, "ids")
+    _need(w_up, h.dtype, "w_up")
+    _need(w_down, h.dtype, "w_down")
+    _need(resid, torch.float32, "resid")
+    experts, ff, width = w_up.shape
+    vocab, top = table.shape
+    _check(
+        mixers().vx_table_experts(_p(h), _code(h.dtype), _pitched(h, "h"), _p(ids), _p(fed),
+                                  0 if fed is None else fed.numel(), _p(table), vocab, top, experts, _p(w_up),
+                                  _p(w_down), width, ff, _p(resid), num_tokens, _p(status), _stream()),
+        "table_experts",
     )

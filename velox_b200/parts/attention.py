@@ -6,6 +6,14 @@ to the cache -> attention of the step's rows over the cache -> output projection
 the cache: the write comes first.  Whether a row belongs to a prompt portion or is a single
 decoded token makes no difference here; the step's work layout decides which kernel family
 runs which rows.
+
+Optional forms, all chosen by parameters: heads whose query/key size and value size differ and
+need not be multiples of 16 (``key_dim``, ``value_dim``: the projections are laid out with every
+head padded with zeros to ``head_dim``, which is what the kernels see); a window that keeps the
+first ``keep_first`` keys; a learned sink per head in the softmax denominator (``sink``); a gate
+per head on the heads' outputs, ``sigmoid(W_g x)`` (``head_gate``: its rows ride along behind
+q | k | v in the one projection).  Such a part takes its matrices as ``q.weight``, ``k.weight``,
+``v.weight`` (and biases) instead of one ``qkv.weight``.
 """
 from __future__ import annotations
 
@@ -46,22 +54,83 @@ class Attention(Mixer):
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
         self.qkv_width = self.q_size + 2 * self.kv_size
-        self.w_qkv = self.expect("qkv.weight", (self.qkv_width, self.hidden_size))
+        self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
+        self.sink = self.expect("sink", (self.num_heads,)) if params.get("sink", False) else None
+        # Rows finished by the merge kernel: that is where a sink and the kept first keys come in.
+        self.anchored = self.sink is not None or self.keep_first > 0
+        self.head_gate = bool(params.get("head_gate", False))
         self.b_qkv = None
         self.b_qkv_lowp = None
-        if params.get("qkv_bias", False):
-            self.b_qkv = self.expect("qkv.bias", (self.qkv_width,))
-            if dtype != torch.float32:
-                self.b_qkv_lowp = self.b_qkv.to(dtype)
-        self.w_out = self.expect("out.weight", (self.hidden_size, self.q_size))
+        if "qkv.weight" in weights:
+            self.proj_width = self.qkv_width
+            self.w_qkv = self.expect("qkv.weight", (self.qkv_width, self.hidden_size))
+            if params.get("qkv_bias", False):
+                self.b_qkv = self.expect("qkv.bias", (self.qkv_width,))
+            self.w_out = self.expect("out.weight", (self.hidden_size, self.q_size))
+        else:
+            self._fuse_padded(params, dtype, device)
+        if self.b_qkv is not None and dtype != torch.float32:
+            self.b_qkv_lowp = self.b_qkv.to(dtype)
         # Compile (or find) the kernels for this head size now, not in the first step.
         kernels.attention_lib(self.head_dim)
 
+    def _fuse_padded(self, params, dtype, device) -> None:
+        """One projection matrix q | k | v | gate from separate tensors whose heads have
+        ``key_dim`` (q, k) and ``value_dim`` (v) rows: every head is padded with rows of zeros to
+        ``head_dim``, the output projection with columns of zeros, and the whole to a multiple of
+        eight rows."""
+        E, H, G, D = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
+        kd = int(params.get("key_dim", D))
+        vd = int(params.get("value_dim", D))
+        if not (0 < kd <= D and 0 < vd <= D):
+            raise ValueError(f"key_dim={kd} and value_dim={vd} must lie within head_dim={D}")
+        self.key_dim, self.value_dim = kd, vd
+
+        def padded_heads(t, heads, size):
+            t = t.reshape(heads, size, *t.shape[1:])
+            if size == D:
+                return t.reshape(heads * D, *t.shape[2:])
+            out = t.new_zeros((heads, D) + tuple(t.shape[2:]))
+            out[:, :size] = t
+            return out.reshape(heads * D, *t.shape[2:])
+
+        pieces = [padded_heads(self.expect("q.weight", (H * kd, E)), H, kd),
+                  padded_heads(self.expect("k.weight", (G * kd, E)), G, kd),
+                  padded_heads(self.expect("v.weight", (G * vd, E)), G, vd)]
+        bias = None
+        if params.get("qkv_bias", False):
+            bias = [padded_heads(self.expect("q.bias", (H * kd,)), H, kd),
+                    padded_heads(self.expect("k.bias", (G * kd,)), G, kd),
+                    padded_heads(self.expect("v.bias", (G * vd,)), G, vd)]
+        if self.head_gate:
+            pieces.append(self.expect("gate.weight", (H, E)))
+            if bias is not None:
+                bias.append(bias[0].new_zeros(H))
+        rows = sum(p.shape[0] for p in pieces)
+        self.proj_width = -(-rows // 8) * 8
+        if self.proj_width != rows:
+            pieces.append(pieces[0].new_zeros(self.proj_width - rows, E))
+            if bias is not None:
+                bias.append(bias[0].new_zeros(self.proj_width - rows))
+        self.w_qkv = torch.cat(pieces).contiguous()
+        if bias is not None:
+            self.b_qkv = torch.cat(bias).contiguous()
+        w_out = self.expect("out.weight", (E, H * vd))
+        if vd != D:
+            wide = w_out.new_zeros(E, H, D)
+            wide[:, :, :vd] = w_out.reshape(E, H, vd)
+            w_out = wide.reshape(E, H * D).contiguous()
+        self.w_out = w_out
+        for name in ("q.weight", "k.weight", "v.weight", "q.bias", "k.bias", "v.bias", "gate.weight"):
+            self.weights.pop(name, None)
+
     def cache_needs(self) -> CacheNeeds:
-        return CacheNeeds(paged=PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window))
+        return CacheNeeds(paged=PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window,
+                                               keep_first=self.keep_first))
 
     def attention_signature(self):
-        return (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window, self.head_dim)
+        base = (self.num_kv_heads, self.num_heads // self.num_kv_heads, self.window, self.head_dim)
+        return base + (self.keep_first, True) if self.anchored else base
 
     # The input is used by the QKV projection only, which can make the norm itself.
     accepts_pending_norm = True
@@ -72,7 +141,7 @@ class Attention(Mixer):
     def forward(self, x, ctx, cache):
         T = ctx.num_tokens
         ws = ctx.workspace
-        qkv = ws.get("attention.qkv", (ws.max_tokens, self.qkv_width), self.dtype)
+        qkv = ws.get(f"attention.qkv{self.proj_width}", (ws.max_tokens, self.proj_width), self.dtype)
         group = ctx.groups[cache.group]
         k_cache, v_cache = (None, None) if cache.read_only else (cache.k, cache.v)
         # Projection, rotation and cache write in one kernel, where the position encoding
@@ -87,7 +156,7 @@ class Attention(Mixer):
             self.position.rotate_and_store(qkv, ctx, group.slot_mapping, k_cache, v_cache,
                                            self.num_heads, self.num_kv_heads)
 
-        attn = ws.get("attention.out", (ws.max_tokens, self.q_size), self.dtype)
+        attn = ws.get(f"attention.out{self.q_size}", (ws.max_tokens, self.q_size), self.dtype)
         plan = ctx.attention_plan(cache.group, self.attention_signature())
         for kind, items, count in plan.launches:
             kernels.attention(
@@ -99,6 +168,7 @@ class Attention(Mixer):
                 cluster=(plan.cluster if kind == kernels.ATTN_BF16_NARROW else
                          getattr(plan, "tc_ctas_per_sm", 1) if kind == kernels.ATTN_BF16_TC else 1),
                 layout_checked=getattr(plan, "checked", False),
+                keep_first=self.keep_first,
             )
         if hasattr(plan, "checked"):
             plan.checked = True
@@ -106,8 +176,11 @@ class Attention(Mixer):
             kernels.attention_merge(
                 attn, ctx.q_start, plan.merge_items, plan.num_merges, plan.partial_o,
                 plan.partial_lse, self.num_heads, self.num_kv_heads, self.head_dim,
-                max_rows=plan.merge_rows,
+                max_rows=plan.merge_rows, sinks=self.sink,
             )
+        if self.head_gate:
+            kernels.head_gate(attn, qkv[:, self.qkv_width : self.qkv_width + self.num_heads], T,
+                              self.num_heads, self.head_dim)
 
         if ctx.residual is not None and use_tensor_core_kernel(attn, self.w_out, T):
             # Few tokens: the projection is added straight into the float32 residual stream.

@@ -55,6 +55,8 @@ class PagedCacheSpec:
     # The cached rows serve as keys and as values (a cached latent): no value pages exist and
     # ``LayerCache.v`` is ``LayerCache.k``.
     values_in_keys: bool = False
+    # With a window: the first ``keep_first`` keys stay visible (and cached) for ever.
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

@@ -158,3 +158,34 @@ class PostNormBlock:
             mix_out=mix_out if mixing else None, sums=sums, sums_bias=bias,
             compute_dtype=None if sums is None else lowp.dtype,
         )
+
+
+@register_part("block", "parallel")
+class ParallelBlock:
+    """One norm, and both sublayers read its output:  ``h = norm(x);  x <- x + (mixer(h) +
+    feed_forward(h))``.  A layer may have no feed-forward.  The sums are float32: a part adds its
+    product into the stream itself where it can (``ctx.residual``), what it returns instead is
+    added here, and the last product may stay pending for the next norm to add."""
+
+    def __init__(self, mixer, feed_forward, norms, params=None) -> None:
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norm = norms["input"]
+
+    def forward(self, hidden: HiddenState, ctx, cache) -> None:
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        normed = ws.get("block.normed", (ws.max_tokens, hidden.resid.shape[1]), self.mixer.dtype)
+        self.norm.forward(hidden.resid, hidden.delta, normed, T)
+        hidden.delta = None
+        ctx.residual = hidden.resid
+        ctx.residual_mirror = None
+        ctx.residual_mirror_written = False
+        mixed = self.mixer.forward(normed, ctx, cache)
+        if self.feed_forward is None:
+            hidden.delta = mixed
+        else:
+            if mixed is not None:
+                kernels.residual_add(hidden.resid, mixed, T)
+            hidden.delta = self.feed_forward.forward(normed, ctx)
+        ctx.residual = None

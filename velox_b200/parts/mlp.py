@@ -134,3 +134,134 @@ class DenseXielu(FeedForward):
         out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(act, self.w_down, self.b_down, out, T, self.b_down_lowp, status=ctx.status)
         return out
+
+
+def _pad_to(t: torch.Tensor, dim: int, multiple: int = 8) -> torch.Tensor:
+    size = t.shape[dim]
+    wide = -(-size // multiple) * multiple
+    if wide == size:
+        return t.contiguous()
+    shape = list(t.shape)
+    shape[dim] = wide - size
+    return torch.cat([t, t.new_zeros(shape)], dim=dim).contiguous()
+
+
+@register_part("feed_forward", "dense_act")
+class DenseAct(FeedForward):
+    """``down(act(up(x)))`` without biases; ``activation`` is ``gelu_tanh`` (0.5 z (1 + tanh(
+    sqrt(2/pi) (z + 0.044715 z^3)))), ``relu_squared`` or ``silu``, computed in float32.
+
+    ``gate_rows`` > 0: that many further rows of ``up.weight`` (behind the feed-forward's own) are
+    a gate over the result: the part's product is ``sigmoid(gate . x) * down(...)``, one number per
+    token (``gate_rows`` is 1), added to the residual stream by the part itself."""
+
+    takes_padded_steps = True
+
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        from .recurrent import activation_code
+
+        self.hidden_size = E = int(params["hidden_size"])
+        self.intermediate_size = F = int(params["intermediate_size"])
+        self.act = activation_code(params.get("activation", "gelu_tanh"))
+        self.gate_rows = int(params.get("gate_rows", 0))
+        if self.gate_rows not in (0, 1):
+            raise ValueError("dense_act: gate_rows is 0 or 1")
+        self.w_up = _pad_to(self.expect("up.weight", (F + self.gate_rows, E)), 0)
+        self.up_width = self.w_up.shape[0]
+        # The activated rows are padded with zeros to whole 16-byte rows; the matching columns of
+        # the down projection are zero.
+        self.w_down = _pad_to(self.expect("down.weight", (E, F)), 1)
+        self.act_width = self.w_down.shape[1]
+        kernels.mixers()
+
+    def forward(self, x, ctx):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        if hasattr(x, "materialize"):
+            x = x.materialize()
+        up = ws.get(f"dense_act.up{self.up_width}", (ws.max_tokens, self.up_width), self.dtype)
+        linear(x, self.w_up, None, up, T, status=ctx.status)
+        act = ws.get(f"dense_act.act{self.intermediate_size}_{self.act_width}", (ws.max_tokens, self.act_width),
+                     self.dtype)
+        kernels.act_rows(up[:, : self.intermediate_size], act[:, : self.intermediate_size], T, self.act)
+        if self.gate_rows:
+            down = ws.get(f"dense_act.down{self.hidden_size}", (ws.max_tokens, self.hidden_size), self.dtype)
+            linear(act, self.w_down, None, down, T, status=ctx.status)
+            gate = up[:, self.intermediate_size : self.intermediate_size + 1]
+            if ctx.residual is not None:
+                kernels.gated_rows_add(ctx.residual, down, gate, T)
+                return None
+            sums = ws.get(f"dense_act.sums{self.hidden_size}", (ws.max_tokens, self.hidden_size), torch.float32)
+            sums[:T].zero_()
+            kernels.gated_rows_add(sums, down, gate, T)
+            return _lowered(sums, ws, self.dtype, T, "dense_act.gated")
+        if (ctx.residual is not None and ctx.status is not None and self.dtype != torch.float32
+                and use_tensor_core_kernel(act, self.w_down, T)):
+            linear(act, self.w_down, None, ctx.residual, T, status=ctx.status, accumulate=True)
+            return None
+        out = ws.get("feed_forward.out", (ws.max_tokens, self.hidden_size), self.dtype)
+        linear(act, self.w_down, None, out, T, status=ctx.status)
+        return out
+
+
+def _lowered(sums: torch.Tensor, ws, dtype, num_rows: int, name: str) -> torch.Tensor:
+    """float32 rows in the compute dtype (for a block that has offered no stream to add into)."""
+    if dtype == torch.float32:
+        return sums
+    out = ws.get(name, tuple(sums.shape), dtype)
+    kernels.cast_f32_to_bf16(sums, out, num_rows * sums.shape[1])
+    return out
+
+
+@register_part("feed_forward", "table_experts")
+class TableExperts(FeedForward):
+    """``experts`` small feed-forwards ``down_e(relu(up_e(x))^2)`` without biases, of which every
+    token uses ``top``: row ``token id`` of an integer ``table`` [vocab, top] names them (there
+    is no router), each with weight 1 / top.  ``up.weight`` / ``down.weight`` are the experts'
+    matrices one after the other.  ``shared``: parameters of a ``dense_act`` part that runs for
+    every token beside them (its weights carry the prefix ``shared.``).
+
+    The part adds its result into the float32 residual stream itself."""
+
+    takes_padded_steps = True
+
+    def __init__(self, params, weights, dtype, device) -> None:
+        super().__init__(params, weights, dtype, device)
+        self.hidden_size = E = int(params["hidden_size"])
+        self.experts = X = int(params["experts"])
+        self.top = int(params["top"])
+        self.expert_ff = F = int(params["expert_ff"])
+        self.vocab_size = int(params["vocab_size"])
+        if not 0 < self.top <= X:
+            raise ValueError(f"top={self.top} must lie within experts={X}")
+        self.w_up = self.expect("up.weight", (X * F, E)).view(X, F, E)
+        self.w_down = self.expect("down.weight", (X * E, F)).view(X, E, F)
+        self.table = self.expect("table", (self.vocab_size, self.top))
+        self.shared = None
+        if params.get("shared"):
+            own = {name[len("shared."):]: t for name, t in weights.items() if name.startswith("shared.")}
+            self.shared = DenseAct(params["shared"], own, dtype, device)
+        kernels.mixers()
+
+    def forward(self, x, ctx):
+        T = ctx.num_tokens
+        ws = ctx.workspace
+        if hasattr(x, "materialize"):
+            x = x.materialize()
+        stream = ctx.residual
+        target = stream
+        if target is None:
+            target = ws.get(f"table_experts.sums{self.hidden_size}", (ws.max_tokens, self.hidden_size), torch.float32)
+            target[:T].zero_()
+        kernels.table_experts(x, ctx.token_ids, getattr(ctx, "fed_tokens", None), self.table, self.w_up,
+                              self.w_down, target, T, ctx.status)
+        if self.shared is not None:
+            ctx.residual = target
+            product = self.shared.forward(x, ctx)
+            ctx.residual = stream
+            if product is not None:
+                kernels.residual_add(target, product, T)
+        if stream is not None:
+            return None
+        return _lowered(target, ws, self.dtype, T, "table_experts.out")

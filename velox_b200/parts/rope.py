@@ -56,6 +56,11 @@ class NoPosition(PositionEncoding):
         self.head_dim = int(params["head_dim"])
 
     def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
+        if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * self.head_dim:
+            # The projection's rows hold more than q | k | v: the kernel that takes a row pitch.
+            kernels.pair_rope_cache_write(qkv, ctx.positions, None, None, slots, k_cache, v_cache, ctx.num_tokens,
+                                          num_heads, num_kv_heads, self.head_dim, 0, ctx.status)
+            return
         kernels.rope_cache_write(
             qkv, ctx.positions, None, None, slots, k_cache, v_cache, ctx.num_tokens,
             num_heads, num_kv_heads, self.head_dim, 0, ctx.status,
@@ -68,7 +73,14 @@ class RotaryInterleaved(PositionEncoding):
     of a vector are a pair ``(u, v) -> (u cos a - v sin a, v cos a + u sin a)`` with ``a =
     position * base^(-2i / rotary_dim)``; the other dims pass.  The part owns the float32 tables
     ``cos``/``sin`` [max_position, rotary_dim / 2] (angles formed in float64, rounded once); the
-    mixer that applies it passes them to its kernel."""
+    mixer that applies it passes them to its kernel, or calls ``rotate_and_store`` (``head_dim``
+    given), which rotates q in place and k on its way into the paged cache.
+
+    ``scaling`` = {factor, original, fast, slow} stretches the slow pairs (YaRN): with
+    ``turn(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln base)``, ``lo = max(floor(turn(fast)),
+    0)``, ``hi = min(ceil(turn(slow)), rotary_dim - 1)`` and ``ramp_i = clamp((i - lo) / max(hi -
+    lo, 0.001), 0, 1)``, pair i turns by ``f_i / factor * ramp_i + f_i * (1 - ramp_i)`` per
+    position, and cos and sin are multiplied by ``0.1 ln(factor) + 1``."""
 
     def __init__(self, params, weights, dtype, device) -> None:
         super().__init__(params, weights, dtype, device)
@@ -80,12 +92,35 @@ class RotaryInterleaved(PositionEncoding):
         pairs = self.rotary_dim // 2
         exponent = torch.arange(pairs, dtype=torch.float64) * (2.0 / max(self.rotary_dim, 1))
         inv_freq = torch.pow(torch.tensor(self.base, dtype=torch.float64), -exponent)
+        self.head_dim = int(params["head_dim"]) if params.get("head_dim") else None
+        magnitude = 1.0
+        scaling = params.get("scaling")
+        if scaling:
+            import math
+
+            factor, original = float(scaling["factor"]), float(scaling["original"])
+
+            def turn(turns: float) -> float:
+                return self.rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+            lo = max(math.floor(turn(float(scaling["fast"]))), 0)
+            hi = min(math.ceil(turn(float(scaling["slow"]))), self.rotary_dim - 1)
+            ramp = ((torch.arange(pairs, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            inv_freq = inv_freq / factor * ramp + inv_freq * (1.0 - ramp)
+            magnitude = 0.1 * math.log(factor) + 1.0
         angles = torch.outer(torch.arange(self.max_position, dtype=torch.float64), inv_freq)
         width = max(pairs, 1)
         cos = torch.ones((self.max_position, width), dtype=torch.float32)
         sin = torch.zeros((self.max_position, width), dtype=torch.float32)
-        cos[:, :pairs] = angles.cos().to(torch.float32)
-        sin[:, :pairs] = angles.sin().to(torch.float32)
+        cos[:, :pairs] = (angles.cos() * magnitude).to(torch.float32)
+        sin[:, :pairs] = (angles.sin() * magnitude).to(torch.float32)
         self.pairs = pairs
         self.cos = cos.to(device).contiguous()
         self.sin = sin.to(device).contiguous()
+
+    def rotate_and_store(self, qkv, ctx, slots, k_cache, v_cache, num_heads, num_kv_heads):
+        if self.head_dim is None:
+            raise ValueError("rotary_interleaved needs head_dim to rotate heads of a q | k | v projection")
+        kernels.pair_rope_cache_write(qkv, ctx.positions, self.cos, self.sin, slots, k_cache, v_cache,
+                                      ctx.num_tokens, num_heads, num_kv_heads, self.head_dim,
+                                      self.rotary_dim if self.pairs else 0, ctx.status)

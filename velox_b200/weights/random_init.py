@@ -8,7 +8,8 @@ checkpoint (src/weight_loader.py:139-155).
 Every tensor is drawn from its own generator, keyed by (seed, tensor name), so a tensor's
 values do not depend on which other tensors exist or on the order they are made in.  Matrices
 and biases are N(0, std); norm weights are 1 + N(0, std) so that a missing norm multiply shows;
-the weights of a weighted sum are 1/n + N(0, std).
+the weights of a weighted sum are 1/n + N(0, std); an integer table gets rows of different
+numbers below its bound.
 """
 from __future__ import annotations
 
@@ -39,6 +40,12 @@ def tensor_seed(seed: int, name: str) -> int:
 def random_tensor(source: TensorSource, seed: int, std: float, dtype: torch.dtype) -> torch.Tensor:
     generator = torch.Generator(device="cpu")
     generator.manual_seed(tensor_seed(seed, source.name))
+    if source.init.startswith("distinct_below:"):
+        # An integer table whose rows hold different numbers below a bound (a token's experts).
+        bound = int(source.init.split(":", 1)[1])
+        rows, picks = source.shape
+        order = torch.rand((rows, bound), generator=generator).argsort(dim=1)
+        return order[:, :picks].to(torch.int32).contiguous()
     values = torch.empty(source.shape, dtype=torch.float32)
     values.normal_(0.0, std, generator=generator)
     if source.init == "one_plus_normal":
@@ -46,6 +53,10 @@ def random_tensor(source: TensorSource, seed: int, std: float, dtype: torch.dtyp
     elif source.init == "average_plus_normal":
         # Weights of a sum over the tensor's entries that keeps the scale of what it sums.
         values += 1.0 / max(values.numel(), 1)
+    elif source.init == "normal_wide":
+        # Small matrices inside a recurrence (gates, short convolutions): an order of magnitude
+        # above the projections' scale, so that their effect shows.
+        values *= 10.0
     elif source.init != "normal":
         raise ValueError(f"unknown init {source.init!r} for {source.name}")
     return values.to(dtype)
