@@ -635,9 +635,11 @@ def _reference_numbers(args, ref_root):
 
 
 def run_compare(args):
-    """``--compare-designs SIZE,...``: one layer of the Peratar design beside one layer of the
-    Qwen2 design at the same width, head count and feed-forward weight count (the presets
-    ``peratar-<size>`` and ``<size>`` of ``velox_b200.config.presets``), random weights.  Per
+    """``--compare-designs SIZE,...``: one layer of the Peratar design and one of the Redalix design
+    beside one layer of the Qwen2 design at the same width, head count and feed-forward weight
+    count per token (the presets ``peratar-<size>``, ``redalix-<size>`` and ``<size>`` of
+    ``velox_b200.config.presets``), random weights.  A Redalix "layer" is the mean over one period
+    of its pattern of four layers.  Per
     design and size: the time of a decode layer (``--batch`` requests behind 4,096 keys) against
     its bytes and the measured copy bandwidth, the time of a 2,048-token prompt layer against its
     operations and the measured library bf16 rate, and the time a layer spends in every kind of
@@ -652,7 +654,10 @@ def run_compare(args):
     few, many = 2, 6
     rows = []
     for size in args.compare_designs.split(","):
-        for name in (size, "peratar-" + size):
+        for name in (size, "peratar-" + size, "redalix-" + size):
+            if args.designs and name.split("-")[0] not in args.designs.split(",") and not (
+                    "-" not in name and "qwen2" in args.designs.split(",")):
+                continue
             cfg = model_size(name)
             cfg["vocab" if "vocab" in cfg else "vocab_size"] = 8192
             cfg.pop("tie_word_embeddings", None)
@@ -666,7 +671,8 @@ def run_compare(args):
             prefill_s = (long - short) / (many - few) * 1e-3
             flops = roofline.layer_flops(cfg, PREFILL_TOKENS, 0)
             row = {
-                "design": "Peratar" if name.startswith("peratar-") else "Qwen2", "size": size,
+                "design": "Peratar" if name.startswith("peratar-") else "Redalix" if name.startswith("redalix-") else "Qwen2",
+                "size": size,
                 "decode": {"batch": args.batch, "keys": keys, "us_per_layer": round(decode_s * 1e6, 1),
                            "layer_bytes": weights + cached, "us_by_bytes": round((weights + cached) / (peaks["hbm_gbs"] * 1e9) * 1e6, 1),
                            "hbm_frac": round((weights + cached) / decode_s / 1e9 / peaks["hbm_gbs"], 3),
@@ -699,8 +705,10 @@ def main():
     parser.add_argument("--impl", default="own", choices=["own", "reference"])
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip the batch 1 / 64 points")
     parser.add_argument("--compare-designs", default=None, metavar="SIZE,...",
-                        help="instead of the benchmark: one layer of the Peratar design beside one of the Qwen2 design "
-                             "at the named sizes (0.5b, 1.5b, 3b, 7b), decode and prefill")
+                        help="instead of the benchmark: one layer of the Peratar and Redalix designs beside one of the "
+                             "Qwen2 design at the named sizes (0.5b, 1.5b, 3b), decode and prefill")
+    parser.add_argument("--designs", default=None, metavar="NAME,...",
+                        help="with --compare-designs: only these designs (qwen2, peratar, redalix)")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 or world > 1:

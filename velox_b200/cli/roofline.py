@@ -51,11 +51,76 @@ def _latent_layers(config_json: Dict) -> Optional[List[Dict]]:
     return config_json.get("layers")
 
 
+def _is_redalix(config_json: Dict) -> bool:
+    return config_json.get("architecture") == "Redalix" or "Redalix" in (config_json.get("architectures") or [])
+
+
+def _redalix_attention(m: Dict, width: int) -> Tuple[int, int, int]:
+    """(weights, cached values per key, rounded head size) of one windowed attention mixer."""
+    head = -(-max(m["dim"], m["vdim"]) // 16) * 16
+    weights = width * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"])) + m["heads"] * m["vdim"] * width
+    if "rot" in m:
+        weights += m["heads"] * width  # the gate per head
+    return weights, 2 * m["kv_heads"] * head, head
+
+
+def _redalix_layer(entry: Dict, width: int, tokens: int, batch: int, context: int):
+    """(weights read, bytes of cache and state touched, operations) of one layer for ``tokens``
+    new tokens of each of ``batch`` sequences behind ``context`` keys.  Experts: as many as the
+    step's tokens can name; a window bounds the keys a token reads; a state is read and written."""
+    kind, m = entry["type"], entry["mixer"]
+    weights = cache = 0
+    flops = 0.0
+    rows = batch * tokens
+
+    def attention(a):
+        nonlocal weights, cache, flops
+        w, per_key, head = _redalix_attention(a, width)
+        weights += w
+        reach = a["mask"]["size"] + a["mask"].get("keep_first", 0)
+        cache += batch * min(context + tokens, reach + tokens) * per_key * 2
+        pairs = sum(min(context + i + 1, reach) for i in range(tokens)) if tokens <= 4096 else tokens * reach
+        flops += 2.0 * rows * w + 4.0 * batch * pairs * a["heads"] * head
+
+    if kind == "attention":
+        attention(m)
+    elif kind == "parallel":
+        attention(m["left"])
+        r = m["right"]
+        part = r["width"] // r["blocks"]
+        weights += 3 * r["width"] * width
+        flops += 2.0 * rows * 3 * r["width"] * width + 2.0 * rows * 2 * r["width"] * part
+        weights += 2 * 2 * r["width"] * part  # the two gate matrices are float32
+        cache += batch * r["conv"] * r["width"] * 4 * 2
+    else:
+        inner = m["heads"] * m["vdim"]
+        rows_in = 2 * inner + 2 * m["groups"] * m["state"] + m["heads"]
+        weights += rows_in * width + inner * width
+        flops += 2.0 * rows * (rows_in + inner) * width + 6.0 * rows * inner * m["state"]
+        cache += batch * (m["heads"] * m["state"] * m["vdim"] + (m["conv"] - 1) * (inner + 2 * m["groups"] * m["state"])) * 4 * 2
+    mlp = entry.get("mlp")
+    if mlp is not None:
+        if mlp["kind"] == "dense":
+            weights += 2 * mlp["ff"] * width
+            flops += 2.0 * rows * 2 * mlp["ff"] * width
+        else:
+            used = min(mlp["router"]["experts"], rows * mlp["router"]["top"])
+            weights += used * 2 * mlp["expert"]["ff"] * width
+            flops += 2.0 * rows * mlp["router"]["top"] * 2 * mlp["expert"]["ff"] * width
+            if mlp.get("shared"):
+                weights += (2 * mlp["shared"]["ff"] + 1) * width
+                flops += 2.0 * rows * 2 * mlp["shared"]["ff"] * width
+    return 2 * weights, cache, flops
+
+
 def layer_bytes(config_json: Dict, batch: int, context: int) -> Tuple[int, int]:
     """(bytes of one layer's matrices in bfloat16, bytes of ``batch`` x ``context`` cached rows of
     one layer: keys and values, or the latent rows that serve as both), averaged over the layers
     of a configuration that lists them."""
     entries = _latent_layers(config_json)
+    if entries is not None and _is_redalix(config_json):
+        parts = [_redalix_layer(entry, config_json["width"], 1, batch, context) for entry in entries]
+        return sum(p[0] for p in parts) // len(parts), sum(p[1] for p in parts) // len(parts)
     if entries is not None:
         width = config_json["width"]
         weights = cache = 0
@@ -81,6 +146,8 @@ def layer_flops(config_json: Dict, tokens: int, context: int) -> float:
     (for latent attention: as the engine computes it, scores and sums over the cached rows)."""
     entries = _latent_layers(config_json)
     pairs = tokens * (context + (tokens + 1) / 2.0)
+    if entries is not None and _is_redalix(config_json):
+        return sum(_redalix_layer(entry, config_json["width"], tokens, 1, context)[2] for entry in entries) / len(entries)
     if entries is not None:
         weights, _ = layer_bytes(config_json, 0, 0)
         attention = 0.0

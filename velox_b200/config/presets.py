@@ -1,5 +1,5 @@
-"""Named example configurations of the Qwen2.5 dense family, and of the Peratar design at the same
-widths, as ``config.json`` dictionaries.
+"""Named example configurations of the Qwen2.5 dense family, and of the Peratar and Redalix designs
+at the same widths, as ``config.json`` dictionaries.
 
 They exist for runs with random weights (``--model-size`` of the benchmark command line): no
 checkpoint is needed to time the layer sizes of a published model.  Nothing in the engine
@@ -77,7 +77,61 @@ def _peratar_tiny() -> Dict[str, Any]:
             "layers": layers, "max_position_embeddings": 512}
 
 
+def _redalix(like: str, experts: int = 16, top: int = 2) -> Dict[str, Any]:
+    """A Redalix configuration with the width, head counts, layer count and vocabulary of the named
+    Qwen2.5 size.  Its layers repeat the pattern parallel, attention, parallel, mamba2; attention
+    heads are as wide as that model's; the recurrence is as wide as the model, in eight parts; the
+    state-space layer has twice the model's width in heads of 64 values over a state of 128; every
+    feed-forward is ``experts`` experts of a quarter of that model's inner width, ``top`` per
+    token, beside a shared expert of the whole inner width, so that a token meets as many
+    feed-forward weights as in the gated feed-forward of that size."""
+    base = MODEL_SIZES[like]
+    width, heads, kv_heads = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
+    head = base.get("head_dim") or width // heads
+    inner = base["intermediate_size"]
+    mlp = {"kind": "moe", "expert": {"ff": max(64, inner // 4 // 64 * 64)}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": inner}}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+            "mask": {"size": 1024, "keep_first": 64}}
+    right = {"width": width, "blocks": 8, "conv": 4}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                 "mask": {"size": 4096},
+                 "rot": {"base": base["rope_theta"], "dims": head,
+                         "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mamba = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 2, "norm_groups": 2, "conv": 4}
+    pattern = [
+        {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp},
+        {"type": "attention", "mixer": attention, "mlp": mlp},
+        {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp},
+        {"type": "mamba2", "mixer": mamba, "mlp": mlp},
+    ]
+    entries = [copy.deepcopy(pattern[index % len(pattern)]) for index in range(base["num_hidden_layers"])]
+    return {"architecture": "Redalix", "vocab": base["vocab_size"], "width": width, "norm": {"eps": 1e-5},
+            "layers": entries, "max_position_embeddings": base["max_position_embeddings"]}
+
+
+def _redalix_tiny() -> Dict[str, Any]:
+    """A tiny Redalix configuration for smoke runs of the command lines: one layer of each kind."""
+    left = {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 32, "scale": 0.25, "mask": {"size": 24, "keep_first": 4}}
+    attention = {"heads": 4, "kv_heads": 1, "dim": 32, "vdim": 16, "scale": 0.18, "mask": {"size": 40},
+                 "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 1.0}}}
+    mlp = {"kind": "moe", "expert": {"ff": 48}, "router": {"experts": 6, "top": 2}, "shared": {"ff": 64}}
+    layers = [
+        {"type": "parallel", "mixer": {"left": left, "right": {"width": 96, "blocks": 3, "conv": 4}},
+         "mlp": {"kind": "dense", "ff": 160}},
+        {"type": "attention", "mixer": attention, "mlp": mlp},
+        {"type": "mamba2", "mixer": {"heads": 8, "vdim": 16, "state": 24, "groups": 2, "norm_groups": 2, "conv": 3},
+         "mlp": mlp},
+    ]
+    return {"architecture": "Redalix", "vocab": 384, "width": 128, "norm": {"eps": 1e-5}, "layers": layers,
+            "max_position_embeddings": 512}
+
+
 MODEL_SIZES.update({
+    "tiny-r": _redalix_tiny(),
+    "redalix-0.5b": _redalix("0.5b"),
+    "redalix-1.5b": _redalix("1.5b"),
+    "redalix-3b": _redalix("3b"),
     "tiny-p": _peratar_tiny(),
     "peratar-0.5b": _peratar("0.5b"),
     "peratar-1.5b": _peratar("1.5b"),
