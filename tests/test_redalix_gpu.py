@@ -228,9 +228,54 @@ def test_experts_by_table(dtype, width, ff, experts, top):
         for e in table[token].tolist():
             want[t] += plain.relu_squared(hs[t] @ up[e].double().cpu().numpy().T) @ down[e].double().cpu().numpy().T / top
     status = torch.zeros(4, dtype=torch.int32).cuda()
+    start = resid.clone()
+    loose = float(np.abs(want).max()) * (1 if dtype == "float32" else 30)
     kernels.table_experts(h[:, 8:], ids.cuda(), fed, table, up, down, resid, T, status)
     assert int(status[0]) == 0
-    close(resid, want, "float32", "experts by table", scale=float(np.abs(want).max()) * (1 if dtype == "float32" else 30))
+    close(resid, want, "float32", "experts by table", scale=loose)
+    # the same as matrix-vector products spread over the grid
+    resid2 = start.clone()
+    act = torch.zeros(T * top * ff).cuda()
+    assert kernels.table_experts_rows(h[:, 8:], ids.cuda(), fed, table, up, down, act, resid2, T, status)
+    close(resid2, want, "float32", "experts by table, rows over the grid", scale=loose)
+    # and as tiled products over the pairs ordered by expert (activations rounded to bfloat16)
+    if dtype == "bfloat16" and width % 8 == 0 and ff % 8 == 0:
+        places = kernels.grouped_places(T, top, experts)
+        route = torch.zeros(2 * places + T * top, dtype=torch.int32).cuda()
+        acts = torch.zeros(places, ff, dtype=torch.bfloat16).cuda()
+        rows = torch.zeros(places, width).cuda()
+        resid3 = start.clone()
+        assert kernels.table_experts_grouped(h[:, 8:], ids.cuda(), fed, table, up, down, route, acts, rows, resid3, T, status)
+        close(resid3, want, "float32", "experts by table, grouped", scale=float(np.abs(want).max()) * 3000)
+    assert int(status[0]) == 0
+
+
+@pytest.mark.parametrize("tokens,width,ff,experts,top", [(300, 64, 24, 5, 2), (130, 256, 72, 8, 3), (700, 128, 200, 16, 1)])
+def test_experts_grouped_many_tokens(tokens, width, ff, experts, top):
+    """Runs of many tokens per expert (several tiles, ragged ends, an expert nobody names)."""
+    from velox_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(tokens)
+    vocab = 40
+    h = torch.randn(tokens, width, generator=gen).to(torch.bfloat16).cuda()
+    up = (torch.randn(experts, ff, width, generator=gen) / width ** 0.5).to(torch.bfloat16).cuda()
+    down = (torch.randn(experts, width, ff, generator=gen) / ff ** 0.5).to(torch.bfloat16).cuda()
+    table = torch.rand(vocab, experts - 1, generator=gen).argsort(dim=1)[:, :top].to(torch.int32).contiguous().cuda()
+    ids = torch.randint(0, vocab, (tokens,), generator=gen).to(torch.int32).cuda()
+    resid = torch.randn(tokens, width, generator=gen).cuda()
+    want = resid.double()
+    chosen = table[ids.long()].long()
+    for k in range(top):
+        a = torch.relu(torch.einsum("tw,tfw->tf", h.double(), up.double()[chosen[:, k]])) ** 2
+        want = want + torch.einsum("tf,twf->tw", a.to(torch.bfloat16).double(), down.double()[chosen[:, k]]) / top
+    places = kernels.grouped_places(tokens, top, experts)
+    route = torch.zeros(2 * places + tokens * top, dtype=torch.int32).cuda()
+    acts = torch.zeros(places, ff, dtype=torch.bfloat16).cuda()
+    rows = torch.zeros(places, width).cuda()
+    status = torch.zeros(4, dtype=torch.int32).cuda()
+    assert kernels.table_experts_grouped(h, ids, None, table, up, down, route, acts, rows, resid, tokens, status)
+    assert int(status[0]) == 0
+    close(resid, want.cpu().numpy(), "float32", "grouped experts", scale=float(want.abs().max()) * 300)
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))

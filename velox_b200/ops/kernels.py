@@ -145,6 +145,15 @@ def mixers():
             _ptr, _c_int, _c_ll, _ptr, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _ptr,
             _c_int, _ptr, _ptr,
         ]
+        lib.vx_table_experts_rows.argtypes = [
+            _ptr, _c_int, _c_ll, _ptr, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _ptr,
+            _ptr, _c_int, _ptr, _ptr,
+        ]
+        lib.vx_grouped_tile_rows.restype = _c_int
+        lib.vx_table_experts_grouped.argtypes = [
+            _ptr, _c_ll, _ptr, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _ptr, _c_int,
+            _ptr, _c_ll, _ptr, _ptr, _c_int, _ptr, _ptr,
+        ]
         _mixers = lib
     return _mixers
 
@@ -1375,3 +1384,61 @@ def table_experts(h, ids, fed, table, w_up, w_down, resid, num_tokens, status) -
                                   _p(w_down), width, ff, _p(resid), num_tokens, _p(status), _stream()),
         "table_experts",
     )
+
+
+def table_experts_rows(h, ids, fed, table, w_up, w_down, act, resid, num_tokens, status) -> bool:
+    """``table_experts`` as two launches whose blocks each take some rows of one (token, expert)
+    pair's projection: ``act`` float32 [tokens * top * ff] holds the activations in between.
+    False (nothing done): a row or a token's activations do not fit a block's shared memory."""
+    experts, ff, width = w_up.shape
+    vocab, top = table.shape
+    if width * 4 > 48 * 1024 or top * ff * 4 > 48 * 1024:
+        return False
+    _need(table, torch.int32, "table")
+    _need(ids, torch.int32, "ids")
+    _need(w_up, h.dtype, "w_up")
+    _need(w_down, h.dtype, "w_down")
+    _need(resid, torch.float32, "resid")
+    _need(act, torch.float32, "act")
+    if act.numel() < num_tokens * top * ff:
+        raise ValueError("table_experts_rows: the activation buffer is too small")
+    _check(
+        mixers().vx_table_experts_rows(_p(h), _code(h.dtype), _pitched(h, "h"), _p(ids), _p(fed),
+                                       0 if fed is None else fed.numel(), _p(table), vocab, top, experts, _p(w_up),
+                                       _p(w_down), width, ff, _p(act), _p(resid), num_tokens, _p(status), _stream()),
+        "table_experts_rows",
+    )
+    return True
+
+
+def grouped_places(num_tokens: int, top: int, experts: int) -> int:
+    """Places (rows of the ordered pairs, every expert's run padded to whole tiles) that
+    ``table_experts_grouped`` needs for a step."""
+    tile = int(mixers().vx_grouped_tile_rows())
+    return -(-(num_tokens * top + experts * (tile - 1)) // tile) * tile
+
+
+def table_experts_grouped(h, ids, fed, table, w_up, w_down, route, act, rows, resid, num_tokens, status) -> bool:
+    """``table_experts`` for long bfloat16 steps: the pairs ordered by expert, both projections as
+    tiled tensor-core products.  ``route`` int32 scratch, ``act`` bfloat16 [places, ff],
+    ``rows`` float32 [places, width] (see ``grouped_places``).  False: sizes it does not take."""
+    experts, ff, width = w_up.shape
+    vocab, top = table.shape
+    if h.dtype != torch.bfloat16 or width % 8 or ff % 8 or _pitched(h, "h") % 8 or experts * 12 > 48 * 1024:
+        return False
+    places = grouped_places(num_tokens, top, experts)
+    tile = int(mixers().vx_grouped_tile_rows())
+    if (route.numel() < places // tile + places + num_tokens * top or act.shape[0] < places or rows.shape[0] < places
+            or act.shape[1] != ff or rows.shape[1] != width):
+        raise ValueError("table_experts_grouped: the scratch buffers are too small")
+    _need(route, torch.int32, "route")
+    _need(act, torch.bfloat16, "act")
+    _need(rows, torch.float32, "rows")
+    _need(resid, torch.float32, "resid")
+    _check(
+        mixers().vx_table_experts_grouped(_p(h), _pitched(h, "h"), _p(ids), _p(fed), 0 if fed is None else fed.numel(),
+                                          _p(table), vocab, top, experts, _p(w_up), _p(w_down), width, ff, _p(route),
+                                          places, _p(act), ff, _p(rows), _p(resid), num_tokens, _p(status), _stream()),
+        "table_experts_grouped",
+    )
+    return True

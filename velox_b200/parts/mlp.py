@@ -244,6 +244,28 @@ class TableExperts(FeedForward):
             self.shared = DenseAct(params["shared"], own, dtype, device)
         kernels.mixers()
 
+    # Steps with more tokens than this run the experts as tiled tensor-core products over the
+    # (token, expert) pairs ordered by expert; shorter ones as matrix-vector products spread over
+    # the grid (every pair then reads its expert's matrices once).
+    GROUPED_FROM_TOKENS = 48
+
+    def _experts(self, x, ctx, target, T) -> None:
+        ws = ctx.workspace
+        ids, fed = ctx.token_ids, getattr(ctx, "fed_tokens", None)
+        X, F, E = self.experts, self.expert_ff, self.hidden_size
+        if self.dtype == torch.bfloat16 and T > self.GROUPED_FROM_TOKENS:
+            places = kernels.grouped_places(ws.max_tokens, self.top, X)
+            route = ws.get(f"table_experts.route{places}", (2 * places + ws.max_tokens * self.top,), torch.int32)
+            act = ws.get(f"table_experts.act{F}", (places, F), torch.bfloat16)
+            rows = ws.get(f"table_experts.rows{E}", (places, E), torch.float32)
+            if kernels.table_experts_grouped(x, ids, fed, self.table, self.w_up, self.w_down, route, act, rows,
+                                             target, T, ctx.status):
+                return
+        act = ws.get(f"table_experts.act32_{F}", (ws.max_tokens * self.top * F,), torch.float32)
+        if kernels.table_experts_rows(x, ids, fed, self.table, self.w_up, self.w_down, act, target, T, ctx.status):
+            return
+        kernels.table_experts(x, ids, fed, self.table, self.w_up, self.w_down, target, T, ctx.status)
+
     def forward(self, x, ctx):
         T = ctx.num_tokens
         ws = ctx.workspace
@@ -254,8 +276,7 @@ class TableExperts(FeedForward):
         if target is None:
             target = ws.get(f"table_experts.sums{self.hidden_size}", (ws.max_tokens, self.hidden_size), torch.float32)
             target[:T].zero_()
-        kernels.table_experts(x, ctx.token_ids, getattr(ctx, "fed_tokens", None), self.table, self.w_up,
-                              self.w_down, target, T, ctx.status)
+        self._experts(x, ctx, target, T)
         if self.shared is not None:
             ctx.residual = target
             product = self.shared.forward(x, ctx)
