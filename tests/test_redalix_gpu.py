@@ -122,6 +122,41 @@ def test_recurrence_gates_and_scan(width, blocks):
     assert torch.all(state[0] == 0) and torch.all(state[2] == 0) and torch.all(state[1, :2] == 0)
 
 
+@pytest.mark.parametrize("width", [40, 300])
+def test_recurrence_scan_in_chunks_equals_the_loop(width):
+    """Two sequences of a step, one of several chunks with a ragged end, from states that are not
+    zero: the chunked form against the plain loop, outputs and final states."""
+    from velox_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(width)
+    lengths = [3, 210, 64, 1]
+    T = sum(lengths)
+    a = torch.rand(T, width, generator=gen) * 0.6 + 0.39
+    b = torch.randn(T, width, generator=gen)
+    y = torch.randn(T, width, generator=gen)
+    state = torch.randn(6, width + 3, generator=gen).cuda()
+    before = state.clone()
+    slots = [4, 0, 2, 5]
+    want, row = np.zeros((T, width)), 0
+    final = {}
+    for n, slot in zip(lengths, slots):
+        S = before[slot, 3:].double().cpu().numpy()
+        for i in range(n):
+            S = a[row].double().numpy() * S + b[row].double().numpy()
+            want[row] = S * y[row].double().numpy()
+            row += 1
+        final[slot] = S
+    out = torch.zeros(T, width).cuda()
+    q_start, q_len, seq_slots = step_arrays(lengths, slots)
+    scratch = torch.zeros(kernels.rglru_scan_scratch(T, len(lengths), width)).cuda()
+    kernels.rglru_scan(a.cuda(), b.cuda(), y.cuda(), state[:, 3:], out, q_start, q_len, seq_slots, len(lengths),
+                       kernels.ACT_NONE, scratch=scratch, num_tokens=T)
+    close(out, want, "float32", "chunked scan", scale=float(np.abs(want).max()))
+    for slot, S in final.items():
+        close(state[slot, 3:], S, "float32", f"state of slot {slot}")
+    assert torch.equal(state[1], before[1]) and torch.equal(state[3], before[3]) and torch.equal(state[:, :3], before[:, :3])
+
+
 @pytest.mark.parametrize("heads,groups,N,P", [(4, 2, 12, 8), (3, 1, 7, 20), (8, 2, 64, 32), (2, 2, 128, 64)])
 def test_state_space_scan(heads, groups, N, P):
     from velox_b200.ops import kernels

@@ -163,14 +163,14 @@ __global__ void rglru_gates_kernel(const float* __restrict__ u, long long u_stri
                                    const float* __restrict__ wi_t, const float* __restrict__ bi,
                                    const float* __restrict__ lam, float decay_scale, float* __restrict__ a_out,
                                    float* __restrict__ b_out, long long ab_stride, int num_tokens) {
-  extern __shared__ float u_s[];  // [TT][part]
+  extern __shared__ __align__(16) float u_s[];  // [part][TT]: a thread reads all tokens of one input at once
   allow_dependents();
   grid_dependency_wait();
   const int t0 = blockIdx.x * TT;
   const int blk = blockIdx.y;
   for (int idx = threadIdx.x; idx < TT * part; idx += blockDim.x) {
     const int tt = idx / part, i = idx - tt * part;
-    u_s[idx] = t0 + tt < num_tokens ? u[(size_t)(t0 + tt) * u_stride + (size_t)blk * part + i] : 0.f;
+    u_s[i * TT + tt] = t0 + tt < num_tokens ? u[(size_t)(t0 + tt) * u_stride + (size_t)blk * part + i] : 0.f;
   }
   __syncthreads();
   const float* wa = wa_t + (size_t)blk * part * part;
@@ -180,13 +180,26 @@ __global__ void rglru_gates_kernel(const float* __restrict__ u, long long u_stri
     const int c = blk * part + o;
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) { ar[tt] = ba[c]; ai[tt] = bi[c]; }
+#pragma unroll 4
     for (int i = 0; i < part; ++i) {
       const float wr = wa[(size_t)i * part + o], wg = wi[(size_t)i * part + o];
+      if (TT % 4 == 0) {
+        const float4* u4 = reinterpret_cast<const float4*>(u_s + i * TT);
 #pragma unroll
-      for (int tt = 0; tt < TT; ++tt) {
-        const float uv = u_s[tt * part + i];
-        ar[tt] = fmaf(wr, uv, ar[tt]);
-        ai[tt] = fmaf(wg, uv, ai[tt]);
+        for (int q = 0; q < TT / 4; ++q) {
+          const float4 uv = u4[q];
+          ar[4 * q] = fmaf(wr, uv.x, ar[4 * q]);         ai[4 * q] = fmaf(wg, uv.x, ai[4 * q]);
+          ar[4 * q + 1] = fmaf(wr, uv.y, ar[4 * q + 1]); ai[4 * q + 1] = fmaf(wg, uv.y, ai[4 * q + 1]);
+          ar[4 * q + 2] = fmaf(wr, uv.z, ar[4 * q + 2]); ai[4 * q + 2] = fmaf(wg, uv.z, ai[4 * q + 2]);
+          ar[4 * q + 3] = fmaf(wr, uv.w, ar[4 * q + 3]); ai[4 * q + 3] = fmaf(wg, uv.w, ai[4 * q + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+          const float uv = u_s[i * TT + tt];
+          ar[tt] = fmaf(wr, uv, ar[tt]);
+          ai[tt] = fmaf(wg, uv, ai[tt]);
+        }
       }
     }
     const float sp = sq_softplus(lam[c]);
@@ -198,7 +211,7 @@ __global__ void rglru_gates_kernel(const float* __restrict__ u, long long u_stri
       const float a = expf(log_a);
       const float mult = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f));
       a_out[(size_t)(t0 + tt) * ab_stride + c] = a;
-      b_out[(size_t)(t0 + tt) * ab_stride + c] = mult * g * u_s[tt * part + o];
+      b_out[(size_t)(t0 + tt) * ab_stride + c] = mult * g * u_s[o * TT + tt];
     }
   }
 }
@@ -243,90 +256,187 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a_in, const float* _
   *st = S;
 }
 
-// ---------------------------------------------------------------------------------------------
-// State-space recurrence with a scalar decay per head.  One block per (head, sequence); thread
-// (r, p) keeps SSD_NS state rows n = r * SSD_NS .. of value column p in registers.  Tokens are
-// taken SSD_TC at a time: their B, C, x and dt go to shared memory together.
-constexpr int SSD_NS = 16;
-constexpr int SSD_TC = 8;
+// The same recurrence for long portions, in two launches over chunks of RG_CHUNK tokens: first
+// every chunk's product of decays and its result from a zero state (and, for a sequence's first
+// chunk, a copy of the state it starts from); then every chunk finds its starting state by
+// folding the chunks before it, in order, and runs its tokens.  The chunks of sequence s lie at
+// places q_start[s] / RG_CHUNK + s + c of the summaries.
+constexpr int RG_CHUNK = 64;
+
+__global__ void rglru_chunk_kernel(const float* __restrict__ a_in, const float* __restrict__ b_in,
+                                   long long ab_stride, int width, const float* __restrict__ state,
+                                   long long state_stride, float* __restrict__ prod, float* __restrict__ part,
+                                   float* __restrict__ init, const int* __restrict__ q_start,
+                                   const int* __restrict__ q_len, const int* __restrict__ seq_slots) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = blockIdx.y, s = blockIdx.z;
+  const int n = q_len[s], start = q_start[s];
+  if (ch >= width || c * RG_CHUNK >= n) return;
+  const int lo = c * RG_CHUNK, hi = min(n, lo + RG_CHUNK);
+  float P = 1.f, Q = 0.f;
+  for (int i = lo; i < hi; ++i) {
+    const size_t row = (size_t)(start + i);
+    const float a = a_in[row * ab_stride + ch];
+    Q = fmaf(a, Q, b_in[row * ab_stride + ch]);
+    P *= a;
+  }
+  const size_t place = (size_t)(start / RG_CHUNK + s + c);
+  prod[place * width + ch] = P;
+  part[place * width + ch] = Q;
+  if (c == 0) init[(size_t)s * width + ch] = state[(size_t)seq_slots[s] * state_stride + ch];
+}
 
 template <typename T>
-__global__ void ssd_scan_kernel(const float* __restrict__ xbc, long long xbc_stride, const T* __restrict__ dt_in,
-                                long long dt_stride, const float* __restrict__ dt_bias,
-                                const float* __restrict__ a_log, const float* __restrict__ d_skip,
-                                float* __restrict__ state, long long state_stride, float* __restrict__ y_out,
-                                long long y_stride, int heads, int groups, int N, int P,
-                                const int* __restrict__ q_start, const int* __restrict__ q_len,
-                                const int* __restrict__ seq_slots) {
+__global__ void rglru_apply_kernel(const float* __restrict__ a_in, const float* __restrict__ b_in,
+                                   long long ab_stride, const T* __restrict__ y, long long y_stride, int width,
+                                   float* __restrict__ state, long long state_stride,
+                                   const float* __restrict__ prod, const float* __restrict__ part,
+                                   const float* __restrict__ init, T* __restrict__ out, long long out_stride,
+                                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ seq_slots, int y_act) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int ch = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = blockIdx.y, s = blockIdx.z;
+  const int n = q_len[s], start = q_start[s];
+  if (ch >= width || c * RG_CHUNK >= n) return;
+  const size_t first = (size_t)(start / RG_CHUNK + s);
+  float S = init[(size_t)s * width + ch];
+  for (int k = 0; k < c; ++k) S = fmaf(prod[(first + k) * width + ch], S, part[(first + k) * width + ch]);
+  const int lo = c * RG_CHUNK, hi = min(n, lo + RG_CHUNK);
+  for (int i = lo; i < hi; ++i) {
+    const size_t row = (size_t)(start + i);
+    S = fmaf(a_in[row * ab_stride + ch], S, b_in[row * ab_stride + ch]);
+    out[row * out_stride + ch] = from_float<T>(S * sq_act(to_float(y[row * y_stride + ch]), y_act));
+  }
+  if (hi == n) state[(size_t)seq_slots[s] * state_stride + ch] = S;
+}
+
+// ---------------------------------------------------------------------------------------------
+// State-space recurrence with a scalar decay per head.  The columns of a head's state (one per
+// value dim p) never meet: y[p] = sum_n S[n, p] C[n].  A block takes SSD_WARPS * 32 / RL columns of
+// one head of one sequence; RL lanes of a warp share a column, each keeping up to SSD_NS state
+// rows of it in registers, and their shares of y meet by warp shuffles, so the token loop has no
+// block barrier.  Tokens are taken SSD_TC at a time: their B, C, x and dt go to shared memory
+// together, the next ones while these are used (two buffers).
+constexpr int SSD_NS = 16;
+constexpr int SSD_TC = 16;
+constexpr int SSD_WARPS = 4;
+
+template <typename T, int RL>
+__global__ void __launch_bounds__(SSD_WARPS * 32) ssd_scan_kernel(
+    const float* __restrict__ xbc, long long xbc_stride, const T* __restrict__ dt_in, long long dt_stride,
+    const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+    float* __restrict__ state, long long state_stride, float* __restrict__ y_out, long long y_stride, int heads,
+    int groups, int N, int P, int col_blocks, const int* __restrict__ q_start, const int* __restrict__ q_len,
+    const int* __restrict__ seq_slots) {
   extern __shared__ float ssd_s[];
   allow_dependents();
   grid_dependency_wait();
-  const int h = blockIdx.x, s = blockIdx.y;
+  constexpr int COLS = SSD_WARPS * 32 / RL;  // columns of a block
+  const int h = blockIdx.x / col_blocks, p0 = (blockIdx.x - h * col_blocks) * COLS;
+  const int s = blockIdx.y;
   const int n_tok = q_len[s], start = q_start[s];
   if (n_tok <= 0) return;
-  const int R = (N + SSD_NS - 1) / SSD_NS;
   const int tid = threadIdx.x;
-  const int r = tid / P, p = tid - r * P;
+  const int r = tid % RL, col = tid / RL, p = p0 + col;
+  const bool live = p < P;
   const int g = h / (heads / groups);
   const int inner = heads * P;
-  float* b_s = ssd_s;                    // [TC][N]
-  float* c_s = b_s + SSD_TC * N;         // [TC][N]
-  float* x_s = c_s + SSD_TC * N;         // [TC][P]
-  float* dt_s = x_s + SSD_TC * P;        // [TC] dt, [TC] decay
-  float* part_s = dt_s + 2 * SSD_TC;     // [TC][R][P]
+  const int NP = RL * SSD_NS;  // padded state rows
+  // Two buffers of: B [TC][NP], C [TC][NP], x [TC][COLS], dt [TC], decay [TC].
+  const int buf_floats = 2 * SSD_TC * NP + SSD_TC * COLS + 2 * SSD_TC;
   float* st = state + (size_t)seq_slots[s] * state_stride + (size_t)h * N * P;
   float S[SSD_NS];
 #pragma unroll
   for (int k = 0; k < SSD_NS; ++k) {
     const int n = r * SSD_NS + k;
-    S[k] = (r < R && n < N) ? st[(size_t)n * P + p] : 0.f;
+    S[k] = (live && n < N) ? st[(size_t)n * P + p] : 0.f;
   }
   const float neg_a = -expf(a_log[h]);
   const float bias = dt_bias[h], dskip = d_skip[h];
-  for (int i0 = 0; i0 < n_tok; i0 += SSD_TC) {
+  // What a thread fetches of the next tokens while these are used: it waits for the values only
+  // when it puts them into the other buffer, after the token loop.
+  constexpr int THREADS = SSD_WARPS * 32;
+  constexpr int BC_PER = 2 * SSD_TC * RL * SSD_NS / THREADS;
+  constexpr int X_PER = (SSD_TC * COLS + THREADS - 1) / THREADS;
+  float pre_bc[BC_PER], pre_x[X_PER], pre_dt = 0.f;
+  auto fetch = [&](int i0) {
     const int tc = min(SSD_TC, n_tok - i0);
-    __syncthreads();
-    for (int idx = tid; idx < tc * N; idx += blockDim.x) {
-      const int k = idx / N, n = idx - k * N;
-      const float* row = xbc + (size_t)(start + i0 + k) * xbc_stride;
-      b_s[k * N + n] = row[inner + g * N + n];
-      c_s[k * N + n] = row[inner + groups * N + g * N + n];
+#pragma unroll
+    for (int u = 0; u < BC_PER; ++u) {
+      const int idx = tid + u * THREADS;
+      const int arr = idx / (SSD_TC * NP), rem = idx - arr * (SSD_TC * NP);
+      const int k = rem / NP, n = rem - k * NP;
+      pre_bc[u] = (k < tc && n < N)
+                      ? xbc[(size_t)(start + i0 + k) * xbc_stride + inner + arr * groups * N + g * N + n]
+                      : 0.f;
     }
-    for (int idx = tid; idx < tc * P; idx += blockDim.x) {
-      const int k = idx / P, q = idx - k * P;
-      x_s[k * P + q] = xbc[(size_t)(start + i0 + k) * xbc_stride + (size_t)h * P + q];
+#pragma unroll
+    for (int u = 0; u < X_PER; ++u) {
+      const int idx = tid + u * THREADS;
+      const int k = idx / COLS, q = idx - k * COLS;
+      pre_x[u] = (k < tc && p0 + q < P) ? xbc[(size_t)(start + i0 + k) * xbc_stride + (size_t)h * P + p0 + q] : 0.f;
     }
-    if (tid < tc) {
-      const float dt = sq_softplus(to_float(dt_in[(size_t)(start + i0 + tid) * dt_stride + h]) + bias);
+    if (tid < tc) pre_dt = to_float(dt_in[(size_t)(start + i0 + tid) * dt_stride + h]);
+  };
+  auto put = [&](float* buf) {
+#pragma unroll
+    for (int u = 0; u < BC_PER; ++u) buf[tid + u * THREADS] = pre_bc[u];  // B then C, as fetched
+    float* x_s = buf + 2 * SSD_TC * NP;
+#pragma unroll
+    for (int u = 0; u < X_PER; ++u)
+      if (tid + u * THREADS < SSD_TC * COLS) x_s[tid + u * THREADS] = pre_x[u];
+    if (tid < SSD_TC) {
+      float* dt_s = x_s + SSD_TC * COLS;
+      const float dt = sq_softplus(pre_dt + bias);
       dt_s[tid] = dt;
       dt_s[SSD_TC + tid] = expf(neg_a * dt);
     }
-    __syncthreads();
-    if (r < R) {
-      for (int k = 0; k < tc; ++k) {
-        const float dt = dt_s[k], decay = dt_s[SSD_TC + k];
-        const float xin = dt * x_s[k * P + p];
-        float acc = 0.f;
-#pragma unroll
-        for (int j = 0; j < SSD_NS; ++j) {
-          const int n = r * SSD_NS + j;
-          if (n < N) {
-            S[j] = fmaf(decay, S[j], b_s[k * N + n] * xin);
-            acc = fmaf(S[j], c_s[k * N + n], acc);
-          }
-        }
-        part_s[(k * R + r) * P + p] = acc;
-      }
-    }
-    __syncthreads();
-    for (int idx = tid; idx < tc * P; idx += blockDim.x) {
-      const int k = idx / P, q = idx - k * P;
+  };
+  fetch(0);
+  put(ssd_s);
+  __syncthreads();
+  int which = 0;
+  for (int i0 = 0; i0 < n_tok; i0 += SSD_TC) {
+    const int tc = min(SSD_TC, n_tok - i0);
+    float* buf = ssd_s + which * buf_floats;
+    const bool more = i0 + SSD_TC < n_tok;
+    if (more) fetch(i0 + SSD_TC);
+    const float* b_s = buf;
+    const float* c_s = b_s + SSD_TC * NP;
+    const float* x_s = c_s + SSD_TC * NP;
+    const float* dt_s = x_s + SSD_TC * COLS;
+    for (int k = 0; k < tc; ++k) {
+      const float dt = dt_s[k], decay = dt_s[SSD_TC + k];
+      const float xv = x_s[k * COLS + col];
+      const float xin = dt * xv;
+      const float4* b4 = reinterpret_cast<const float4*>(b_s + k * NP + r * SSD_NS);
+      const float4* c4 = reinterpret_cast<const float4*>(c_s + k * NP + r * SSD_NS);
       float acc = 0.f;
-      for (int rr = 0; rr < R; ++rr) acc += part_s[(k * R + rr) * P + q];
-      y_out[(size_t)(start + i0 + k) * y_stride + (size_t)h * P + q] = acc + dskip * x_s[k * P + q];
+#pragma unroll
+      for (int j = 0; j < SSD_NS / 4; ++j) {
+        const float4 bv = b4[j], cv = c4[j];
+        S[4 * j] = fmaf(decay, S[4 * j], bv.x * xin);
+        acc = fmaf(S[4 * j], cv.x, acc);
+        S[4 * j + 1] = fmaf(decay, S[4 * j + 1], bv.y * xin);
+        acc = fmaf(S[4 * j + 1], cv.y, acc);
+        S[4 * j + 2] = fmaf(decay, S[4 * j + 2], bv.z * xin);
+        acc = fmaf(S[4 * j + 2], cv.z, acc);
+        S[4 * j + 3] = fmaf(decay, S[4 * j + 3], bv.w * xin);
+        acc = fmaf(S[4 * j + 3], cv.w, acc);
+      }
+#pragma unroll
+      for (int off = RL / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (r == 0 && live) y_out[(size_t)(start + i0 + k) * y_stride + (size_t)h * P + p] = acc + dskip * xv;
     }
+    if (more) put(ssd_s + (which ^ 1) * buf_floats);
+    __syncthreads();  // the next tokens are in place, and these may be overwritten
+    which ^= 1;
   }
-  if (r < R) {
+  if (live) {
 #pragma unroll
     for (int k = 0; k < SSD_NS; ++k) {
       const int n = r * SSD_NS + k;
@@ -393,6 +503,27 @@ __global__ void act_rows_kernel(const T* __restrict__ x, long long x_stride, T* 
     const long long t = idx / width;
     const int i = (int)(idx - t * width);
     out[t * out_stride + i] = from_float<T>(sq_act(to_float(x[t * x_stride + i]), kind));
+  }
+}
+
+// bfloat16 rows whose starts and widths are whole 16-byte chunks: eight values a thread.
+__global__ void act_rows_vec_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
+                                    __nv_bfloat16* __restrict__ out, long long out_stride, int chunks,
+                                    long long total, int kind) {
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / chunks;
+    const int i = (int)(idx - t * chunks) * 8;
+    uint4 raw = *reinterpret_cast<const uint4*>(x + t * x_stride + i);
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(pairs[k]);
+      pairs[k] = __floats2bfloat162_rn(sq_act(f.x, kind), sq_act(f.y, kind));
+    }
+    *reinterpret_cast<uint4*>(out + t * out_stride + i) = raw;
   }
 }
 
@@ -502,15 +633,53 @@ VX_API int vx_rglru_gates(const float* u, long long u_stride, int width, int blo
   return (int)cudaGetLastError();
 }
 
+VX_API int vx_rglru_chunk_rows() { return RG_CHUNK; }
+
+// scratch (float32, or null for the one-launch form): 2 * (num_tokens / RG_CHUNK + num_seqs + 1)
+// * width floats for the chunks' summaries and num_seqs * width for the starting states.
 VX_API int vx_rglru_scan(const float* a_in, const float* b_in, long long ab_stride, const void* y, int dtype,
                          long long y_stride, int width, float* state, long long state_stride, void* out,
                          long long out_stride, const int* q_start, const int* q_len, const int* seq_slots,
-                         int num_seqs, int y_act, cudaStream_t stream) {
+                         int num_seqs, int y_act, float* scratch, int num_tokens, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
+  if (scratch != nullptr && num_tokens > RG_CHUNK) {
+    const size_t places = (size_t)(num_tokens / RG_CHUNK + num_seqs + 1);
+    float* prod = scratch;
+    float* part = prod + places * width;
+    float* init = part + places * width;
+    const dim3 grid((width + 127) / 128, (num_tokens + RG_CHUNK - 1) / RG_CHUNK, num_seqs);
+    launch_pdl(rglru_chunk_kernel, grid, dim3(128), 0, stream, a_in, b_in, ab_stride, width, (const float*)state,
+               state_stride, prod, part, init, q_start, q_len, seq_slots);
+    VX_BY_DTYPE(dtype, launch_pdl(rglru_apply_kernel<T>, grid, dim3(128), 0, stream, a_in, b_in, ab_stride,
+                                  (const T*)y, y_stride, width, state, state_stride, (const float*)prod,
+                                  (const float*)part, (const float*)init, (T*)out, out_stride, q_start, q_len,
+                                  seq_slots, y_act));
+    return (int)cudaGetLastError();
+  }
   const dim3 grid((width + 63) / 64, num_seqs);
   VX_BY_DTYPE(dtype, launch_pdl(rglru_scan_kernel<T>, grid, dim3(64), 0, stream, a_in, b_in, ab_stride,
                                 (const T*)y, y_stride, width, state, state_stride, (T*)out, out_stride, q_start,
                                 q_len, seq_slots, y_act));
+  return (int)cudaGetLastError();
+}
+
+template <typename T, int RL>
+static int launch_ssd(const float* xbc, long long xbc_stride, const void* dt_in, long long dt_stride,
+                      const float* dt_bias, const float* a_log, const float* d_skip, float* state,
+                      long long state_stride, float* y_out, long long y_stride, int heads, int groups, int N, int P,
+                      const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, cudaStream_t stream) {
+  constexpr int COLS = SSD_WARPS * 32 / RL;
+  const int col_blocks = (P + COLS - 1) / COLS;
+  const size_t smem = sizeof(float) * 2 * ((size_t)2 * SSD_TC * RL * SSD_NS + (size_t)SSD_TC * COLS + 2 * SSD_TC);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  launch_pdl(ssd_scan_kernel<T, RL>, dim3(heads * col_blocks, num_seqs), dim3(SSD_WARPS * 32), smem, stream, xbc,
+             xbc_stride, (const T*)dt_in, dt_stride, dt_bias, a_log, d_skip, state, state_stride, y_out, y_stride, heads,
+             groups, N, P, col_blocks, q_start, q_len, seq_slots);
   return (int)cudaGetLastError();
 }
 
@@ -520,16 +689,18 @@ VX_API int vx_ssd_scan(const float* xbc, long long xbc_stride, const void* dt_in
                        int P, const int* q_start, const int* q_len, const int* seq_slots, int num_seqs,
                        cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
-  const int R = (N + SSD_NS - 1) / SSD_NS;
-  const int threads = (R * P + 31) / 32 * 32;
-  if (threads > 1024 || threads < SSD_TC) return (int)cudaErrorInvalidValue;
-  const size_t smem = sizeof(float) * ((size_t)2 * SSD_TC * N + (size_t)SSD_TC * P + 2 * SSD_TC +
-                                       (size_t)SSD_TC * R * P);
-  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-  VX_BY_DTYPE(dtype, launch_pdl(ssd_scan_kernel<T>, dim3(heads, num_seqs), dim3(threads), smem, stream, xbc,
-                                xbc_stride, (const T*)dt_in, dt_stride, dt_bias, a_log, d_skip, state, state_stride,
-                                y_out, y_stride, heads, groups, N, P, q_start, q_len, seq_slots));
-  return (int)cudaGetLastError();
+  if (N > 32 * SSD_NS) return (int)cudaErrorInvalidValue;
+#define VX_SSD(RL)                                                                                              \
+  VX_BY_DTYPE(dtype, return (launch_ssd<T, RL>(xbc, xbc_stride, dt_in, dt_stride, dt_bias, a_log, d_skip, state, \
+                                               state_stride, y_out, y_stride, heads, groups, N, P, q_start,     \
+                                               q_len, seq_slots, num_seqs, stream)))
+  if (N <= SSD_NS) { VX_SSD(1); }
+  if (N <= 2 * SSD_NS) { VX_SSD(2); }
+  if (N <= 4 * SSD_NS) { VX_SSD(4); }
+  if (N <= 8 * SSD_NS) { VX_SSD(8); }
+  if (N <= 16 * SSD_NS) { VX_SSD(16); }
+  VX_SSD(32);
+#undef VX_SSD
 }
 
 VX_API int vx_gated_group_norm(const float* y, long long y_stride, const void* z, int dtype, long long z_stride,
@@ -557,6 +728,12 @@ VX_API int vx_act_rows(const void* x, int dtype, long long x_stride, void* out, 
                        int num_tokens, int kind, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const long long total = (long long)num_tokens * width;
+  if (dtype == VX_DTYPE_BF16 && width % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    launch_pdl(act_rows_vec_kernel, dim3(grid_for(total / 8, 256)), dim3(256), 0, stream, (const __nv_bfloat16*)x,
+               x_stride, (__nv_bfloat16*)out, out_stride, width / 8, total / 8, kind);
+    return (int)cudaGetLastError();
+  }
   VX_BY_DTYPE(dtype, launch_pdl(act_rows_kernel<T>, dim3(grid_for(total, 256)), dim3(256), 0, stream, (const T*)x,
                                 x_stride, (T*)out, out_stride, width, total, kind));
   return (int)cudaGetLastError();

@@ -128,8 +128,9 @@ def mixers():
         ]
         lib.vx_rglru_scan.argtypes = [
             _ptr, _ptr, _c_ll, _ptr, _c_int, _c_ll, _c_int, _ptr, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _c_int,
-            _c_int, _ptr,
+            _c_int, _ptr, _c_int, _ptr,
         ]
+        lib.vx_rglru_chunk_rows.restype = _c_int
         lib.vx_ssd_scan.argtypes = [
             _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int,
             _c_int, _ptr, _ptr, _ptr, _c_int, _ptr,
@@ -1290,14 +1291,28 @@ def rglru_gates(u, w_a_t, b_a, w_i_t, b_i, lam, decay_scale, a_out, b_out, num_t
     )
 
 
-def rglru_scan(a_in, b_in, y, state, out, q_start, q_len, seq_slots, num_seqs, y_act) -> None:
+def rglru_scan_scratch(num_tokens: int, num_seqs: int, width: int) -> int:
+    """float32 entries of scratch that ``rglru_scan`` needs to run a step's long portions in
+    chunks."""
+    chunk = int(mixers().vx_rglru_chunk_rows())
+    return (2 * (num_tokens // chunk + num_seqs + 1) + num_seqs) * width
+
+
+def rglru_scan(a_in, b_in, y, state, out, q_start, q_len, seq_slots, num_seqs, y_act, scratch=None,
+               num_tokens=0) -> None:
     """S <- a S + b over every sequence's tokens from the state of its slot (float32
-    [slots, width]); out = S * act(y)."""
+    [slots, width]); out = S * act(y).  With ``scratch`` (float32, ``rglru_scan_scratch`` entries)
+    and ``num_tokens`` (the step's tokens) a long step runs in chunks of tokens side by side."""
     width = a_in.shape[1]
+    if scratch is not None:
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < rglru_scan_scratch(num_tokens, num_seqs, width):
+            raise ValueError("rglru_scan: the scratch is too small")
     _check(
         mixers().vx_rglru_scan(_p(a_in), _p(b_in), _pitched(a_in, "a_in"), _p(y), _code(y.dtype), _pitched(y, "y"),
                                width, _p(state), _pitched(state, "state"), _p(out), _pitched(out, "out"),
-                               _p(q_start), _p(q_len), _p(seq_slots), num_seqs, y_act, _stream()),
+                               _p(q_start), _p(q_len), _p(seq_slots), num_seqs, y_act, _p(scratch), int(num_tokens),
+                               _stream()),
         "rglru_scan",
     )
 

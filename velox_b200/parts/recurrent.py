@@ -105,8 +105,13 @@ class GatedLinearRecurrence(Mixer):
         kernels.rglru_gates(u, self.gate_a_t, self.gate_a_b, self.gate_i_t, self.gate_i_b, self.lam,
                             self.decay_scale, a, b, T)
         gated = ws.get(f"recurrence.gated{W}", (ws.max_tokens, W), self.dtype)
+        scratch = None
+        if T > ctx.num_seqs:
+            # Portions: long ones run in chunks of tokens side by side.
+            size = kernels.rglru_scan_scratch(ws.max_tokens, state.shape[0], W)
+            scratch = ws.get(f"recurrence.chunks{W}", (size,), torch.float32)
         kernels.rglru_scan(a, b, proj[:, :W], state[:, self.conv_elems : self.conv_elems + W], gated, ctx.q_start,
-                           ctx.q_len, ctx.seq_slots, ctx.num_seqs, self.branch_act)
+                           ctx.q_len, ctx.seq_slots, ctx.num_seqs, self.branch_act, scratch=scratch, num_tokens=T)
         out = ws.get(f"recurrence.out{self.hidden_size}", (ws.max_tokens, self.hidden_size), self.dtype)
         linear(gated, self.w_out, None, out, T, status=ctx.status)
         return out
@@ -144,9 +149,8 @@ class StateSpace(Mixer):
         self.w_out = self.expect("out.weight", (E, inner))
         self.conv_elems = (self.taps - 1) * C
         self.state_elems = H * N * P
-        threads = -(-N // 16) * P
-        if threads > 1024:
-            raise ValueError(f"state_size={N} x value_dim={P} is more than the scan kernel's block holds")
+        if N > 512:
+            raise ValueError(f"state_size={N} is more than the scan kernel holds in a warp's registers (512)")
         kernels.mixers()
 
     def cache_needs(self) -> CacheNeeds:
