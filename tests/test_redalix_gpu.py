@@ -110,7 +110,7 @@ def test_recurrence_gates_and_scan(width, blocks):
         a_buf, b_buf = torch.zeros(n, width).cuda(), torch.zeros(n, width).cuda()
         kernels.rglru_gates(u[start : start + n].cuda(), ra.transpose(1, 2).contiguous().cuda(), ba.reshape(-1).cuda(),
                             ri.transpose(1, 2).contiguous().cuda(), bi.reshape(-1).cuda(), lam.cuda(), 8.0, a_buf,
-                            b_buf, n)
+                            b_buf, n, w_a=ra.cuda(), w_i=ri.cuda())
         out = torch.zeros(n, width).cuda()
         q_start, q_len, slots = step_arrays([n], [1])
         kernels.rglru_scan(a_buf, b_buf, y[start : start + n].cuda(), state[:, 2 : 2 + width], out, q_start, q_len, slots,
@@ -192,6 +192,33 @@ def test_state_space_scan(heads, groups, N, P):
     close(torch.from_numpy(got), want.reshape(T, inner), "float32", "state-space scan", scale=float(np.abs(want).max()))
     close(state[1], final.reshape(-1), "float32", "final state")
     assert torch.all(state[0] == 0)
+
+
+def test_state_space_scan_in_chunks_equals_one_block_per_sequence():
+    """Sequences of several chunks with ragged ends beside short ones, from states that are not
+    zero: the three-launch form gives what the one-launch form gives."""
+    from velox_b200.ops import kernels
+
+    gen = torch.Generator().manual_seed(5)
+    heads, groups, N, P = 4, 2, 24, 16
+    lengths, slots = [2, 700, 256, 1, 300], [3, 0, 5, 1, 4]
+    T, inner = sum(lengths), heads * P
+    xbc = torch.randn(T, inner + 2 * groups * N, generator=gen).cuda()
+    dt_raw = torch.randn(T, heads, generator=gen).cuda()
+    dt_bias, a_log, d = (torch.randn(heads, generator=gen) - 1).cuda(), (0.7 * torch.randn(heads, generator=gen) - 2).cuda(), torch.randn(heads, generator=gen).cuda()
+    state0 = torch.randn(7, heads * N * P, generator=gen).cuda()
+    q_start, q_len, seq_slots = step_arrays(lengths, slots)
+    results = []
+    for chunked in (False, True):
+        state = state0.clone()
+        y = torch.zeros(T, inner).cuda()
+        scratch = torch.zeros(kernels.ssd_scan_scratch(T, len(lengths), heads, N, P)).cuda() if chunked else None
+        kernels.ssd_scan(xbc, dt_raw, dt_bias, a_log, d, state, y, heads, groups, N, P, q_start, q_len, seq_slots,
+                         len(lengths), scratch=scratch, num_tokens=T)
+        results.append((y.cpu(), state.cpu()))
+    close(results[1][0], results[0][0].numpy(), "float32", "outputs", scale=float(results[0][0].abs().max()) * 4)
+    close(results[1][1], results[0][1].numpy(), "float32", "states", scale=float(results[0][1].abs().max()) * 4)
+    assert torch.equal(results[1][1][2], state0[2].cpu()) and torch.equal(results[1][1][6], state0[6].cpu())
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))

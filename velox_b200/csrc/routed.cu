@@ -34,15 +34,28 @@ template <>
 __device__ __forceinline__ float dot_row<__nv_bfloat16>(const __nv_bfloat16* __restrict__ w,
                                                         const float* __restrict__ v, int n, int lane) {
   float acc = 0.f;
-  if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
-    for (int i = lane * 8; i < n; i += 256) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(w + i);
-      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  if ((n & 7) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0) {
+    // Four 16-byte loads of a lane are under way before the first is used.
+    for (int i0 = lane * 8; i0 < n; i0 += 1024) {
+      uint4 raw[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(pairs[k]);
-        acc = fmaf(f.x, v[i + 2 * k], acc);
-        acc = fmaf(f.y, v[i + 2 * k + 1], acc);
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 256;
+        raw[u] = i < n ? __ldg(reinterpret_cast<const uint4*>(w + i)) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * 256;
+        if (i < n) {
+          const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+          const float4 v0 = *reinterpret_cast<const float4*>(v + i), v1 = *reinterpret_cast<const float4*>(v + i + 4);
+          const float2 f0 = __bfloat1622float2(pairs[0]), f1 = __bfloat1622float2(pairs[1]);
+          const float2 f2 = __bfloat1622float2(pairs[2]), f3 = __bfloat1622float2(pairs[3]);
+          acc = fmaf(f0.x, v0.x, acc); acc = fmaf(f0.y, v0.y, acc);
+          acc = fmaf(f1.x, v0.z, acc); acc = fmaf(f1.y, v0.w, acc);
+          acc = fmaf(f2.x, v1.x, acc); acc = fmaf(f2.y, v1.y, acc);
+          acc = fmaf(f3.x, v1.z, acc); acc = fmaf(f3.y, v1.w, acc);
+        }
       }
     }
   } else {
@@ -57,7 +70,7 @@ __global__ void table_experts_kernel(const T* __restrict__ h, long long h_stride
                                      int vocab, int top, int experts, const T* __restrict__ w_up,
                                      const T* __restrict__ w_down, int width, int ff, float* __restrict__ resid,
                                      int* status) {
-  extern __shared__ float moe_s[];
+  extern __shared__ __align__(16) float moe_s[];
   float* h_s = moe_s;           // [width]
   float* act_s = h_s + width;   // [ff]
   float* sum_s = act_s + ff;    // [width]
@@ -111,7 +124,7 @@ __global__ void expert_up_rows_kernel(const T* __restrict__ h, long long h_strid
                                       const int* __restrict__ fed, int num_fed, const int* __restrict__ table,
                                       int vocab, int top, int experts, const T* __restrict__ w_up, int width, int ff,
                                       int rows_per_block, float* __restrict__ act, int* status) {
-  extern __shared__ float moe_s[];  // [width]
+  extern __shared__ __align__(16) float moe_s[];  // [width]
   allow_dependents();
   grid_dependency_wait();
   const int pair = blockIdx.y, t = pair / top, k = pair - t * top;
@@ -145,7 +158,7 @@ __global__ void expert_down_rows_kernel(const float* __restrict__ act, const int
                                         const int* __restrict__ fed, int num_fed, const int* __restrict__ table,
                                         int vocab, int top, int experts, const T* __restrict__ w_down, int width,
                                         int ff, int rows_per_block, float* __restrict__ resid) {
-  extern __shared__ float moe_s[];  // [top][ff]
+  extern __shared__ __align__(16) float moe_s[];  // [top][ff]
   allow_dependents();
   grid_dependency_wait();
   const int t = blockIdx.y;
@@ -180,7 +193,18 @@ __global__ void expert_down_rows_kernel(const float* __restrict__ act, const int
 //                         of A are gathered by token (up) or are the places themselves (down);
 //                         the up form squares the positive part and writes bfloat16
 //   gather_pairs_kernel   resid[t] += (sum over the token's pairs, in their order) / top
-constexpr int GG_M = 64, GG_N = 64, GG_K = 32, GG_LD = GG_K + 8;
+constexpr int GG_M = 64, GG_N = 128, GG_K = 64, GG_LD = GG_K + 8, GG_STAGES = 2;
+constexpr int GG_STAGE_ELEMS = (GG_M + GG_N) * GG_LD;
+constexpr size_t GG_SMEM_BYTES = (size_t)GG_STAGES * GG_STAGE_ELEMS * sizeof(__nv_bfloat16);
+
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = valid ? 16 : 0;  // 0: the sixteen bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int LEFT>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(LEFT) : "memory"); }
 
 __global__ void route_pairs_kernel(const int* __restrict__ ids, const int* __restrict__ fed, int num_fed,
                                    const int* __restrict__ table, int vocab, int top, int experts, int num_tokens,
@@ -239,13 +263,15 @@ __global__ void route_pairs_kernel(const int* __restrict__ ids, const int* __res
   }
 }
 
+// A block of four warps (two by two) makes a tile of GG_M places by GG_N outputs; a warp's share is
+// 32 x 64.  Slabs of GG_K inner values of both operands come into shared memory by asynchronous
+// 16-byte copies, the next slab while this one is multiplied (two stages).
 template <bool UP>
 __global__ void __launch_bounds__(128) grouped_gemm_kernel(
     const __nv_bfloat16* __restrict__ a, long long a_stride, const int* __restrict__ place_token,
     const int* __restrict__ tile_expert, const __nv_bfloat16* __restrict__ w, int N, int K,
     __nv_bfloat16* __restrict__ out_lowp, float* __restrict__ out_f32, long long out_stride) {
-  __shared__ __align__(16) __nv_bfloat16 a_s[GG_M * GG_LD];
-  __shared__ __align__(16) __nv_bfloat16 b_s[GG_N * GG_LD];
+  extern __shared__ __align__(16) __nv_bfloat16 gg_s[];
   __shared__ int row_of[GG_M];
   allow_dependents();
   grid_dependency_wait();
@@ -254,6 +280,7 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(
   if (e < 0) return;
   const int n0 = blockIdx.y * GG_N;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 1, wn = warp & 1;
   if (tid < GG_M) {
     const int place = tile * GG_M + tid;
     const int token = place_token[place];
@@ -261,82 +288,101 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(
   }
   __syncthreads();
   const __nv_bfloat16* wb = w + (size_t)e * N * K;
-  float acc[8][4];
+  float acc[2][8][4];
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) acc[j][i] = 0.f;
-  // Each thread moves two 16-byte chunks of A and two of B per slab: row = idx / 4, chunk = idx % 4.
-  uint4 ra[2], rb[2];
-  auto fetch = [&](int k0) {
+    for (int j = 0; j < 8; ++j)
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int idx = tid + u * 128, r = idx >> 2, c = (idx & 3) * 8;
-      ra[u] = make_uint4(0u, 0u, 0u, 0u);
-      rb[u] = make_uint4(0u, 0u, 0u, 0u);
+      for (int i = 0; i < 4; ++i) acc[m][j][i] = 0.f;
+  // Rows of a slab are eight 16-byte chunks; a thread copies chunk tid % 8 of rows tid / 8 + 16 u.
+  const int chunk = (tid & 7) * 8, row0 = tid >> 3;
+  auto fetch = [&](int k0, int stage) {
+    __nv_bfloat16* a_s = gg_s + stage * GG_STAGE_ELEMS;
+    __nv_bfloat16* b_s = a_s + GG_M * GG_LD;
+    const bool k_ok = k0 + chunk < K;
+#pragma unroll
+    for (int u = 0; u < GG_M / 16; ++u) {
+      const int r = row0 + 16 * u;
       const int row = row_of[r];
-      if (row >= 0 && k0 + c < K) ra[u] = *reinterpret_cast<const uint4*>(a + (size_t)row * a_stride + k0 + c);
-      if (n0 + r < N && k0 + c < K) rb[u] = *reinterpret_cast<const uint4*>(wb + (size_t)(n0 + r) * K + k0 + c);
+      const bool ok = k_ok && row >= 0;
+      cp_async_16(a_s + r * GG_LD + chunk, ok ? a + (size_t)row * a_stride + k0 + chunk : a, ok);
     }
-  };
-  fetch(0);
-  for (int k0 = 0; k0 < K; k0 += GG_K) {
-    __syncthreads();
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int idx = tid + u * 128, r = idx >> 2, c = (idx & 3) * 8;
-      *reinterpret_cast<uint4*>(a_s + r * GG_LD + c) = ra[u];
-      *reinterpret_cast<uint4*>(b_s + r * GG_LD + c) = rb[u];
+    for (int u = 0; u < GG_N / 16; ++u) {
+      const int r = row0 + 16 * u;
+      const bool ok = k_ok && n0 + r < N;
+      cp_async_16(b_s + r * GG_LD + chunk, ok ? wb + (size_t)(n0 + r) * K + k0 + chunk : wb, ok);
+    }
+    cp_async_commit();
+  };
+  const int slabs = (K + GG_K - 1) / GG_K;
+  fetch(0, 0);
+  for (int slab = 0; slab < slabs; ++slab) {
+    const int stage = slab & 1;
+    if (slab + 1 < slabs) {
+      fetch((slab + 1) * GG_K, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncthreads();
-    if (k0 + GG_K < K) fetch(k0 + GG_K);
+    const __nv_bfloat16* a_s = gg_s + stage * GG_STAGE_ELEMS;
+    const __nv_bfloat16* b_s = a_s + GG_M * GG_LD;
 #pragma unroll
     for (int kk = 0; kk < GG_K; kk += 16) {
-      uint32_t fa[4];
-      {
-        const __nv_bfloat16* p = a_s + (warp * 16 + (lane & 15)) * GG_LD + kk + (lane >> 4) * 8;
+      uint32_t fa[2][4];
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        const __nv_bfloat16* p = a_s + (wm * 32 + m * 16 + (lane & 15)) * GG_LD + kk + (lane >> 4) * 8;
         const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                     : "=r"(fa[0]), "=r"(fa[1]), "=r"(fa[2]), "=r"(fa[3]) : "r"(addr));
+                     : "=r"(fa[m][0]), "=r"(fa[m][1]), "=r"(fa[m][2]), "=r"(fa[m][3]) : "r"(addr));
       }
 #pragma unroll
       for (int j = 0; j < 8; j += 2) {
         uint32_t fb[4];
-        const __nv_bfloat16* p = b_s + (j * 8 + (lane & 7) + ((lane >> 4) << 3)) * GG_LD + kk + ((lane >> 3) & 1) * 8;
+        const __nv_bfloat16* p = b_s + (wn * 64 + j * 8 + (lane & 7) + ((lane >> 4) << 3)) * GG_LD + kk + ((lane >> 3) & 1) * 8;
         const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
         asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                      : "=r"(fb[0]), "=r"(fb[1]), "=r"(fb[2]), "=r"(fb[3]) : "r"(addr));
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                     : "+f"(acc[j][0]), "+f"(acc[j][1]), "+f"(acc[j][2]), "+f"(acc[j][3])
-                     : "r"(fa[0]), "r"(fa[1]), "r"(fa[2]), "r"(fa[3]), "r"(fb[0]), "r"(fb[1]));
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                     : "+f"(acc[j + 1][0]), "+f"(acc[j + 1][1]), "+f"(acc[j + 1][2]), "+f"(acc[j + 1][3])
-                     : "r"(fa[0]), "r"(fa[1]), "r"(fa[2]), "r"(fa[3]), "r"(fb[2]), "r"(fb[3]));
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                       : "+f"(acc[m][j][0]), "+f"(acc[m][j][1]), "+f"(acc[m][j][2]), "+f"(acc[m][j][3])
+                       : "r"(fa[m][0]), "r"(fa[m][1]), "r"(fa[m][2]), "r"(fa[m][3]), "r"(fb[0]), "r"(fb[1]));
+          asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                       : "+f"(acc[m][j + 1][0]), "+f"(acc[m][j + 1][1]), "+f"(acc[m][j + 1][2]), "+f"(acc[m][j + 1][3])
+                       : "r"(fa[m][0]), "r"(fa[m][1]), "r"(fa[m][2]), "r"(fa[m][3]), "r"(fb[2]), "r"(fb[3]));
+        }
       }
     }
+    __syncthreads();  // the stage may be overwritten by the copy after next
   }
-  // Thread holds rows g and g + 8 of its warp's sixteen, columns 2 * (lane % 4) + {0, 1} of every n8.
+  // A thread holds rows g and g + 8 of each of its two sixteens, columns 2 * (lane % 4) + {0, 1} of every n8.
   const int g = lane >> 2, c2 = 2 * (lane & 3);
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int r = warp * 16 + g + 8 * half;
-    if (row_of[r] < 0) continue;
-    const size_t place = (size_t)tile * GG_M + r;
+  for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int n = n0 + j * 8 + c2;
-      float v0 = acc[j][2 * half], v1 = acc[j][2 * half + 1];
-      if (UP) {
-        v0 = fmaxf(v0, 0.f); v0 *= v0;
-        v1 = fmaxf(v1, 0.f); v1 *= v1;
-        if (n < N) out_lowp[place * out_stride + n] = __float2bfloat16_rn(v0);
-        if (n + 1 < N) out_lowp[place * out_stride + n + 1] = __float2bfloat16_rn(v1);
-      } else {
-        if (n < N) out_f32[place * out_stride + n] = v0;
-        if (n + 1 < N) out_f32[place * out_stride + n + 1] = v1;
+    for (int half = 0; half < 2; ++half) {
+      const int r = wm * 32 + m * 16 + g + 8 * half;
+      if (row_of[r] < 0) continue;
+      const size_t place = (size_t)tile * GG_M + r;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int n = n0 + wn * 64 + j * 8 + c2;
+        float v0 = acc[m][j][2 * half], v1 = acc[m][j][2 * half + 1];
+        if (UP) {
+          v0 = fmaxf(v0, 0.f); v0 *= v0;
+          v1 = fmaxf(v1, 0.f); v1 *= v1;
+          if (n + 1 < N) *reinterpret_cast<__nv_bfloat162*>(out_lowp + place * out_stride + n) = __floats2bfloat162_rn(v0, v1);
+          else if (n < N) out_lowp[place * out_stride + n] = __float2bfloat16_rn(v0);
+        } else {
+          if (n + 1 < N) *reinterpret_cast<float2*>(out_f32 + place * out_stride + n) = make_float2(v0, v1);
+          else if (n < N) out_f32[place * out_stride + n] = v0;
+        }
       }
     }
-  }
 }
 
 __global__ void gather_pairs_kernel(const float* __restrict__ rows, long long row_stride,
@@ -442,10 +488,20 @@ VX_API int vx_table_experts_grouped(const void* h, long long h_stride, const int
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   launch_pdl(route_pairs_kernel, dim3(1), dim3(1024), smem, stream, ids, fed, num_fed, table, vocab, top, experts,
              num_tokens, capacity, max_tiles, tile_expert, place_token, pair_place, status);
-  launch_pdl(grouped_gemm_kernel<true>, dim3(max_tiles, (ff + GG_N - 1) / GG_N), dim3(128), 0, stream,
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)GG_SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)GG_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  launch_pdl(grouped_gemm_kernel<true>, dim3(max_tiles, (ff + GG_N - 1) / GG_N), dim3(128), GG_SMEM_BYTES, stream,
              (const __nv_bfloat16*)h, h_stride, (const int*)place_token, (const int*)tile_expert,
              (const __nv_bfloat16*)w_up, ff, width, (__nv_bfloat16*)act, (float*)nullptr, act_stride);
-  launch_pdl(grouped_gemm_kernel<false>, dim3(max_tiles, (width + GG_N - 1) / GG_N), dim3(128), 0, stream,
+  launch_pdl(grouped_gemm_kernel<false>, dim3(max_tiles, (width + GG_N - 1) / GG_N), dim3(128), GG_SMEM_BYTES, stream,
              (const __nv_bfloat16*)act, act_stride, (const int*)place_token, (const int*)tile_expert,
              (const __nv_bfloat16*)w_down, width, ff, (__nv_bfloat16*)nullptr, rows, (long long)width);
   launch_pdl(gather_pairs_kernel, dim3(num_tokens), dim3(256), 0, stream, (const float*)rows, (long long)width,

@@ -216,6 +216,40 @@ __global__ void rglru_gates_kernel(const float* __restrict__ u, long long u_stri
   }
 }
 
+// The same for a few tokens: one warp per (token, output), the inputs of a part dealt to its
+// lanes; the matrices as stored, [blocks][out][in].
+__global__ void rglru_gates_rows_kernel(const float* __restrict__ u, long long u_stride, int part, int width,
+                                        const float* __restrict__ wa, const float* __restrict__ ba,
+                                        const float* __restrict__ wi, const float* __restrict__ bi,
+                                        const float* __restrict__ lam, float decay_scale, float* __restrict__ a_out,
+                                        float* __restrict__ b_out, long long ab_stride) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int t = blockIdx.y;
+  if (c >= width) return;
+  const int blk = c / part, o = c - blk * part;
+  const float* ur = u + (size_t)t * u_stride + (size_t)blk * part;
+  const float* war = wa + ((size_t)blk * part + o) * part;
+  const float* wir = wi + ((size_t)blk * part + o) * part;
+  float ar = 0.f, ai = 0.f;
+#pragma unroll 4
+  for (int i = lane; i < part; i += 32) {
+    const float uv = ur[i];
+    ar = fmaf(war[i], uv, ar);
+    ai = fmaf(wir[i], uv, ai);
+  }
+  ar = warp_sum(ar) + ba[c];
+  ai = warp_sum(ai) + bi[c];
+  if (lane == 0) {
+    const float r = sq_sigmoid(ar), g = sq_sigmoid(ai);
+    const float log_a = -decay_scale * r * sq_softplus(lam[c]);
+    a_out[(size_t)t * ab_stride + c] = expf(log_a);
+    b_out[(size_t)t * ab_stride + c] = sqrtf(fmaxf(-expm1f(2.0f * log_a), 0.f)) * g * ur[o];
+  }
+}
+
 // S <- a S + b over a sequence's tokens; out = S * gelu(y).  One thread per (channel, sequence).
 template <typename T>
 __global__ void rglru_scan_kernel(const float* __restrict__ a_in, const float* __restrict__ b_in,
@@ -325,42 +359,59 @@ constexpr int SSD_NS = 16;
 constexpr int SSD_TC = 16;
 constexpr int SSD_WARPS = 4;
 
+// Long portions run in chunks of SSD_CHUNK tokens side by side, in three launches: every chunk
+// from a zero state, keeping its last state and the product of its decays (mode 1); per sequence
+// the chunks' starting states, folded in order, and the sequence's new state (ssd_combine_kernel);
+// every chunk again from its starting state, writing y (mode 2).  Mode 0 is a whole sequence in
+// one block: from the slot's state, writing y and the state.  The chunks of sequence s lie at
+// places q_start[s] / SSD_CHUNK + s + c.
+constexpr int SSD_CHUNK = 256;
+constexpr int SSD_SLICE = SSD_NS + 4;  // a lane's B (C) values in shared memory: padded against bank conflicts
+
 template <typename T, int RL>
 __global__ void __launch_bounds__(SSD_WARPS * 32) ssd_scan_kernel(
     const float* __restrict__ xbc, long long xbc_stride, const T* __restrict__ dt_in, long long dt_stride,
     const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
     float* __restrict__ state, long long state_stride, float* __restrict__ y_out, long long y_stride, int heads,
     int groups, int N, int P, int col_blocks, const int* __restrict__ q_start, const int* __restrict__ q_len,
-    const int* __restrict__ seq_slots) {
-  extern __shared__ float ssd_s[];
+    const int* __restrict__ seq_slots, int mode, float* __restrict__ chunk_states,
+    float* __restrict__ chunk_decay) {
+  extern __shared__ __align__(16) float ssd_s[];
   allow_dependents();
   grid_dependency_wait();
   constexpr int COLS = SSD_WARPS * 32 / RL;  // columns of a block
   const int h = blockIdx.x / col_blocks, p0 = (blockIdx.x - h * col_blocks) * COLS;
   const int s = blockIdx.y;
-  const int n_tok = q_len[s], start = q_start[s];
-  if (n_tok <= 0) return;
+  const int seq_tokens = q_len[s], seq_start = q_start[s];
+  const int lo = mode == 0 ? 0 : (int)blockIdx.z * SSD_CHUNK;
+  if (lo >= seq_tokens) return;
+  const int n_tok = mode == 0 ? seq_tokens : min(SSD_CHUNK, seq_tokens - lo);
+  const int start = seq_start + lo;
+  const size_t place = (size_t)(seq_start / SSD_CHUNK + s) + blockIdx.z;
   const int tid = threadIdx.x;
   const int r = tid % RL, col = tid / RL, p = p0 + col;
   const bool live = p < P;
   const int g = h / (heads / groups);
   const int inner = heads * P;
-  const int NP = RL * SSD_NS;  // padded state rows
-  // Two buffers of: B [TC][NP], C [TC][NP], x [TC][COLS], dt [TC], decay [TC].
-  const int buf_floats = 2 * SSD_TC * NP + SSD_TC * COLS + 2 * SSD_TC;
-  float* st = state + (size_t)seq_slots[s] * state_stride + (size_t)h * N * P;
+  constexpr int NP = RL * SSD_NS;      // state rows a block's lanes hold
+  constexpr int NPP = RL * SSD_SLICE;  // their places in shared memory
+  // Two buffers of: B [TC][NPP], C [TC][NPP], x [TC][COLS], dt [TC], decay [TC].
+  const int buf_floats = 2 * SSD_TC * NPP + SSD_TC * COLS + 2 * SSD_TC;
+  float* st = mode == 0 ? state + (size_t)seq_slots[s] * state_stride + (size_t)h * N * P
+                        : chunk_states + (place * heads + h) * (size_t)N * P;
   float S[SSD_NS];
 #pragma unroll
   for (int k = 0; k < SSD_NS; ++k) {
     const int n = r * SSD_NS + k;
-    S[k] = (live && n < N) ? st[(size_t)n * P + p] : 0.f;
+    S[k] = (mode != 1 && live && n < N) ? st[(size_t)n * P + p] : 0.f;
   }
   const float neg_a = -expf(a_log[h]);
   const float bias = dt_bias[h], dskip = d_skip[h];
+  float decay_product = 1.f;
   // What a thread fetches of the next tokens while these are used: it waits for the values only
   // when it puts them into the other buffer, after the token loop.
   constexpr int THREADS = SSD_WARPS * 32;
-  constexpr int BC_PER = 2 * SSD_TC * RL * SSD_NS / THREADS;
+  constexpr int BC_PER = 2 * SSD_TC * NP / THREADS;
   constexpr int X_PER = (SSD_TC * COLS + THREADS - 1) / THREADS;
   float pre_bc[BC_PER], pre_x[X_PER], pre_dt = 0.f;
   auto fetch = [&](int i0) {
@@ -384,8 +435,13 @@ __global__ void __launch_bounds__(SSD_WARPS * 32) ssd_scan_kernel(
   };
   auto put = [&](float* buf) {
 #pragma unroll
-    for (int u = 0; u < BC_PER; ++u) buf[tid + u * THREADS] = pre_bc[u];  // B then C, as fetched
-    float* x_s = buf + 2 * SSD_TC * NP;
+    for (int u = 0; u < BC_PER; ++u) {
+      const int idx = tid + u * THREADS;
+      const int arr = idx / (SSD_TC * NP), rem = idx - arr * (SSD_TC * NP);
+      const int k = rem / NP, n = rem - k * NP;
+      buf[arr * (SSD_TC * NPP) + k * NPP + (n / SSD_NS) * SSD_SLICE + (n % SSD_NS)] = pre_bc[u];
+    }
+    float* x_s = buf + 2 * SSD_TC * NPP;
 #pragma unroll
     for (int u = 0; u < X_PER; ++u)
       if (tid + u * THREADS < SSD_TC * COLS) x_s[tid + u * THREADS] = pre_x[u];
@@ -406,42 +462,76 @@ __global__ void __launch_bounds__(SSD_WARPS * 32) ssd_scan_kernel(
     const bool more = i0 + SSD_TC < n_tok;
     if (more) fetch(i0 + SSD_TC);
     const float* b_s = buf;
-    const float* c_s = b_s + SSD_TC * NP;
-    const float* x_s = c_s + SSD_TC * NP;
+    const float* c_s = b_s + SSD_TC * NPP;
+    const float* x_s = c_s + SSD_TC * NPP;
     const float* dt_s = x_s + SSD_TC * COLS;
     for (int k = 0; k < tc; ++k) {
       const float dt = dt_s[k], decay = dt_s[SSD_TC + k];
       const float xv = x_s[k * COLS + col];
       const float xin = dt * xv;
-      const float4* b4 = reinterpret_cast<const float4*>(b_s + k * NP + r * SSD_NS);
-      const float4* c4 = reinterpret_cast<const float4*>(c_s + k * NP + r * SSD_NS);
-      float acc = 0.f;
+      decay_product *= decay;
+      const float4* b4 = reinterpret_cast<const float4*>(b_s + k * NPP + r * SSD_SLICE);
+      const float4* c4 = reinterpret_cast<const float4*>(c_s + k * NPP + r * SSD_SLICE);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < SSD_NS / 4; ++j) {
         const float4 bv = b4[j], cv = c4[j];
         S[4 * j] = fmaf(decay, S[4 * j], bv.x * xin);
-        acc = fmaf(S[4 * j], cv.x, acc);
         S[4 * j + 1] = fmaf(decay, S[4 * j + 1], bv.y * xin);
-        acc = fmaf(S[4 * j + 1], cv.y, acc);
         S[4 * j + 2] = fmaf(decay, S[4 * j + 2], bv.z * xin);
-        acc = fmaf(S[4 * j + 2], cv.z, acc);
         S[4 * j + 3] = fmaf(decay, S[4 * j + 3], bv.w * xin);
-        acc = fmaf(S[4 * j + 3], cv.w, acc);
+        acc[0] = fmaf(S[4 * j], cv.x, acc[0]);
+        acc[1] = fmaf(S[4 * j + 1], cv.y, acc[1]);
+        acc[2] = fmaf(S[4 * j + 2], cv.z, acc[2]);
+        acc[3] = fmaf(S[4 * j + 3], cv.w, acc[3]);
       }
+      if (mode != 1) {
+        float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
 #pragma unroll
-      for (int off = RL / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-      if (r == 0 && live) y_out[(size_t)(start + i0 + k) * y_stride + (size_t)h * P + p] = acc + dskip * xv;
+        for (int off = RL / 2; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+        if (r == 0 && live) y_out[(size_t)(start + i0 + k) * y_stride + (size_t)h * P + p] = sum + dskip * xv;
+      }
     }
     if (more) put(ssd_s + (which ^ 1) * buf_floats);
     __syncthreads();  // the next tokens are in place, and these may be overwritten
     which ^= 1;
   }
+  if (mode == 2) return;
   if (live) {
 #pragma unroll
     for (int k = 0; k < SSD_NS; ++k) {
       const int n = r * SSD_NS + k;
       if (n < N) st[(size_t)n * P + p] = S[k];
     }
+  }
+  if (mode == 1 && tid == 0 && p0 == 0) chunk_decay[place * heads + h] = decay_product;
+}
+
+// Per sequence: the state its chunks start from, in order, and its new state.  In place: a
+// chunk's own last state (from zero) is replaced by the state it starts from.
+__global__ void ssd_combine_kernel(float* __restrict__ state, long long state_stride, float* __restrict__ chunk_states,
+                                   const float* __restrict__ chunk_decay, int heads, int per_head,
+                                   const int* __restrict__ q_start, const int* __restrict__ q_len,
+                                   const int* __restrict__ seq_slots) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int s = blockIdx.y;
+  const int n = q_len[s];
+  if (n <= 0) return;
+  const size_t total = (size_t)heads * per_head;
+  const size_t first = (size_t)(q_start[s] / SSD_CHUNK + s);
+  const int chunks = (n + SSD_CHUNK - 1) / SSD_CHUNK;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const int h = (int)(e / per_head);
+    float* st = state + (size_t)seq_slots[s] * state_stride + e;
+    float S = *st;
+    for (int c = 0; c < chunks; ++c) {
+      float* at = chunk_states + (first + c) * total + e;
+      const float own = *at;
+      *at = S;
+      S = fmaf(chunk_decay[(first + c) * heads + h], S, own);
+    }
+    *st = S;
   }
 }
 
@@ -605,11 +695,18 @@ VX_API int vx_conv_tokens(const void* x, int dtype, long long x_stride, int chan
   return (int)cudaGetLastError();
 }
 
+// wa, wi: the matrices as stored, [blocks][out][in] (used for a few tokens; may be null).
 VX_API int vx_rglru_gates(const float* u, long long u_stride, int width, int blocks, const float* wa_t,
                           const float* ba, const float* wi_t, const float* bi, const float* lam, float decay_scale,
-                          float* a_out, float* b_out, long long ab_stride, int num_tokens, cudaStream_t stream) {
+                          float* a_out, float* b_out, long long ab_stride, int num_tokens, const float* wa,
+                          const float* wi, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const int part = width / blocks;
+  if (wa != nullptr && wi != nullptr && num_tokens <= 16) {
+    launch_pdl(rglru_gates_rows_kernel, dim3((width + 7) / 8, num_tokens), dim3(256), 0, stream, u, u_stride, part,
+               width, wa, ba, wi, bi, lam, decay_scale, a_out, b_out, ab_stride);
+    return (int)cudaGetLastError();
+  }
   const int threads = part >= 256 ? 256 : (part + 31) / 32 * 32;
   if (num_tokens <= 8) {
     constexpr int TT = 2;
@@ -667,33 +764,57 @@ template <typename T, int RL>
 static int launch_ssd(const float* xbc, long long xbc_stride, const void* dt_in, long long dt_stride,
                       const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                       long long state_stride, float* y_out, long long y_stride, int heads, int groups, int N, int P,
-                      const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, cudaStream_t stream) {
+                      const int* q_start, const int* q_len, const int* seq_slots, int num_seqs, float* scratch,
+                      int num_tokens, cudaStream_t stream) {
   constexpr int COLS = SSD_WARPS * 32 / RL;
   const int col_blocks = (P + COLS - 1) / COLS;
-  const size_t smem = sizeof(float) * 2 * ((size_t)2 * SSD_TC * RL * SSD_NS + (size_t)SSD_TC * COLS + 2 * SSD_TC);
+  const size_t smem = sizeof(float) * 2 * ((size_t)2 * SSD_TC * RL * SSD_SLICE + (size_t)SSD_TC * COLS + 2 * SSD_TC);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  launch_pdl(ssd_scan_kernel<T, RL>, dim3(heads * col_blocks, num_seqs), dim3(SSD_WARPS * 32), smem, stream, xbc,
-             xbc_stride, (const T*)dt_in, dt_stride, dt_bias, a_log, d_skip, state, state_stride, y_out, y_stride, heads,
-             groups, N, P, col_blocks, q_start, q_len, seq_slots);
+  const dim3 block(SSD_WARPS * 32);
+  if (scratch == nullptr || num_tokens <= SSD_CHUNK) {
+    launch_pdl(ssd_scan_kernel<T, RL>, dim3(heads * col_blocks, num_seqs), block, smem, stream, xbc, xbc_stride,
+               (const T*)dt_in, dt_stride, dt_bias, a_log, d_skip, state, state_stride, y_out, y_stride, heads, groups,
+               N, P, col_blocks, q_start, q_len, seq_slots, 0, (float*)nullptr, (float*)nullptr);
+    return (int)cudaGetLastError();
+  }
+  const size_t places = (size_t)(num_tokens / SSD_CHUNK + num_seqs + 1);
+  float* chunk_states = scratch;
+  float* chunk_decay = scratch + places * heads * N * P;
+  const dim3 grid(heads * col_blocks, num_seqs, (num_tokens + SSD_CHUNK - 1) / SSD_CHUNK);
+  launch_pdl(ssd_scan_kernel<T, RL>, grid, block, smem, stream, xbc, xbc_stride, (const T*)dt_in, dt_stride, dt_bias,
+             a_log, d_skip, state, state_stride, y_out, y_stride, heads, groups, N, P, col_blocks, q_start, q_len,
+             seq_slots, 1, chunk_states, chunk_decay);
+  const int per_head = N * P;
+  int cblocks = (int)(((size_t)heads * per_head + 255) / 256);
+  if (cblocks > 148 * 4) cblocks = 148 * 4;
+  launch_pdl(ssd_combine_kernel, dim3(cblocks, num_seqs), dim3(256), 0, stream, state, state_stride, chunk_states,
+             (const float*)chunk_decay, heads, per_head, q_start, q_len, seq_slots);
+  launch_pdl(ssd_scan_kernel<T, RL>, grid, block, smem, stream, xbc, xbc_stride, (const T*)dt_in, dt_stride, dt_bias,
+             a_log, d_skip, state, state_stride, y_out, y_stride, heads, groups, N, P, col_blocks, q_start, q_len,
+             seq_slots, 2, chunk_states, chunk_decay);
   return (int)cudaGetLastError();
 }
 
+VX_API int vx_ssd_chunk_rows() { return SSD_CHUNK; }
+
+// scratch (float32, or null: every sequence in one block per head and column block):
+// (num_tokens / SSD_CHUNK + num_seqs + 1) * heads * (N * P + 1) floats.
 VX_API int vx_ssd_scan(const float* xbc, long long xbc_stride, const void* dt_in, int dtype, long long dt_stride,
                        const float* dt_bias, const float* a_log, const float* d_skip, float* state,
                        long long state_stride, float* y_out, long long y_stride, int heads, int groups, int N,
                        int P, const int* q_start, const int* q_len, const int* seq_slots, int num_seqs,
-                       cudaStream_t stream) {
+                       float* scratch, int num_tokens, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (N > 32 * SSD_NS) return (int)cudaErrorInvalidValue;
 #define VX_SSD(RL)                                                                                              \
   VX_BY_DTYPE(dtype, return (launch_ssd<T, RL>(xbc, xbc_stride, dt_in, dt_stride, dt_bias, a_log, d_skip, state, \
                                                state_stride, y_out, y_stride, heads, groups, N, P, q_start,     \
-                                               q_len, seq_slots, num_seqs, stream)))
+                                               q_len, seq_slots, num_seqs, scratch, num_tokens, stream)))
   if (N <= SSD_NS) { VX_SSD(1); }
   if (N <= 2 * SSD_NS) { VX_SSD(2); }
   if (N <= 4 * SSD_NS) { VX_SSD(4); }

@@ -124,7 +124,8 @@ def mixers():
             _c_int, _c_int, _ptr,
         ]
         lib.vx_rglru_gates.argtypes = [
-            _ptr, _c_ll, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_f, _ptr, _ptr, _c_ll, _c_int, _ptr,
+            _ptr, _c_ll, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_f, _ptr, _ptr, _c_ll, _c_int, _ptr, _ptr,
+            _ptr,
         ]
         lib.vx_rglru_scan.argtypes = [
             _ptr, _ptr, _c_ll, _ptr, _c_int, _c_ll, _c_int, _ptr, _c_ll, _ptr, _c_ll, _ptr, _ptr, _ptr, _c_int,
@@ -133,8 +134,9 @@ def mixers():
         lib.vx_rglru_chunk_rows.restype = _c_int
         lib.vx_ssd_scan.argtypes = [
             _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _ptr, _ptr, _ptr, _c_ll, _ptr, _c_ll, _c_int, _c_int, _c_int,
-            _c_int, _ptr, _ptr, _ptr, _c_int, _ptr,
+            _c_int, _ptr, _ptr, _ptr, _c_int, _ptr, _c_int, _ptr,
         ]
+        lib.vx_ssd_chunk_rows.restype = _c_int
         lib.vx_gated_group_norm.argtypes = [
             _ptr, _c_ll, _ptr, _c_int, _c_ll, _ptr, _c_f, _c_int, _c_int, _ptr, _c_ll, _c_int, _ptr,
         ]
@@ -1277,16 +1279,20 @@ def conv_tokens(x, weight, bias, state, out, q_start, q_len, seq_slots, num_seqs
     )
 
 
-def rglru_gates(u, w_a_t, b_a, w_i_t, b_i, lam, decay_scale, a_out, b_out, num_tokens) -> None:
+def rglru_gates(u, w_a_t, b_a, w_i_t, b_i, lam, decay_scale, a_out, b_out, num_tokens, w_a=None, w_i=None) -> None:
     """Decay and gated input of S <- a S + b from u float32 [tokens, width]; the gate matrices are
-    block-diagonal, stored transposed [blocks, in, out], all float32."""
+    block-diagonal, stored transposed [blocks, in, out], all float32.  ``w_a``, ``w_i``: the same
+    matrices [blocks, out, in], which a step of a few tokens reads instead (a warp per output)."""
     blocks, part, _ = w_a_t.shape
     for name, t in (("w_a_t", w_a_t), ("b_a", b_a), ("w_i_t", w_i_t), ("b_i", b_i), ("lam", lam)):
         _need(t, torch.float32, name)
+    if w_a is not None:
+        _need(w_a, torch.float32, "w_a")
+        _need(w_i, torch.float32, "w_i")
     _check(
         mixers().vx_rglru_gates(_p(u), _pitched(u, "u"), blocks * part, blocks, _p(w_a_t), _p(b_a), _p(w_i_t),
                                 _p(b_i), _p(lam), float(decay_scale), _p(a_out), _p(b_out), _pitched(a_out, "a_out"),
-                                num_tokens, _stream()),
+                                num_tokens, _p(w_a), _p(w_i), _stream()),
         "rglru_gates",
     )
 
@@ -1317,15 +1323,27 @@ def rglru_scan(a_in, b_in, y, state, out, q_start, q_len, seq_slots, num_seqs, y
     )
 
 
+def ssd_scan_scratch(num_tokens: int, num_seqs: int, heads: int, state_size: int, value_dim: int) -> int:
+    """float32 entries of scratch that ``ssd_scan`` needs to run a step's long portions in chunks."""
+    chunk = int(mixers().vx_ssd_chunk_rows())
+    return (num_tokens // chunk + num_seqs + 1) * heads * (state_size * value_dim + 1)
+
+
 def ssd_scan(xbc, dt, dt_bias, a_log, d_skip, state, y_out, heads, groups, state_size, value_dim, q_start, q_len,
-             seq_slots, num_seqs) -> None:
+             seq_slots, num_seqs, scratch=None, num_tokens=0) -> None:
     """Per head: S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + D x with dt = softplus(dt +
-    dt_bias); ``xbc`` float32 rows hold x | B | C, ``state`` float32 [slots, heads * N * P]."""
+    dt_bias); ``xbc`` float32 rows hold x | B | C, ``state`` float32 [slots, heads * N * P].  With
+    ``scratch`` (float32, ``ssd_scan_scratch`` entries) and ``num_tokens`` (the step's tokens) a
+    long step runs in chunks of tokens side by side."""
+    if scratch is not None:
+        _need(scratch, torch.float32, "scratch")
+        if scratch.numel() < ssd_scan_scratch(num_tokens, num_seqs, heads, state_size, value_dim):
+            raise ValueError("ssd_scan: the scratch is too small")
     _check(
         mixers().vx_ssd_scan(_p(xbc), _pitched(xbc, "xbc"), _p(dt), _code(dt.dtype), _pitched(dt, "dt"),
                              _p(dt_bias), _p(a_log), _p(d_skip), _p(state), _pitched(state, "state"), _p(y_out),
                              _pitched(y_out, "y_out"), heads, groups, state_size, value_dim, _p(q_start), _p(q_len),
-                             _p(seq_slots), num_seqs, _stream()),
+                             _p(seq_slots), num_seqs, _p(scratch), int(num_tokens), _stream()),
         "ssd_scan",
     )
 

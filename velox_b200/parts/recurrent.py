@@ -77,8 +77,10 @@ class GatedLinearRecurrence(Mixer):
         self.conv_w = self.expect("conv.weight", (W, self.taps))
         self.conv_b = self.expect("conv.bias", (W,))
         # The gate matrices are stored [block, out, in]; the kernel reads them [block, in, out].
-        self.gate_a_t = self.expect("gate_a.weight", (self.blocks, part, part)).transpose(1, 2).contiguous()
-        self.gate_i_t = self.expect("gate_i.weight", (self.blocks, part, part)).transpose(1, 2).contiguous()
+        self.gate_a = self.expect("gate_a.weight", (self.blocks, part, part))
+        self.gate_i = self.expect("gate_i.weight", (self.blocks, part, part))
+        self.gate_a_t = self.gate_a.transpose(1, 2).contiguous()
+        self.gate_i_t = self.gate_i.transpose(1, 2).contiguous()
         self.gate_a_b = self.expect("gate_a.bias", (self.blocks, part)).reshape(-1).contiguous()
         self.gate_i_b = self.expect("gate_i.bias", (self.blocks, part)).reshape(-1).contiguous()
         self.lam = self.expect("lam", (W,))
@@ -103,7 +105,7 @@ class GatedLinearRecurrence(Mixer):
         a = ws.get(f"recurrence.a{W}", (ws.max_tokens, W), torch.float32)
         b = ws.get(f"recurrence.b{W}", (ws.max_tokens, W), torch.float32)
         kernels.rglru_gates(u, self.gate_a_t, self.gate_a_b, self.gate_i_t, self.gate_i_b, self.lam,
-                            self.decay_scale, a, b, T)
+                            self.decay_scale, a, b, T, w_a=self.gate_a, w_i=self.gate_i)
         gated = ws.get(f"recurrence.gated{W}", (ws.max_tokens, W), self.dtype)
         scratch = None
         if T > ctx.num_seqs:
@@ -168,9 +170,15 @@ class StateSpace(Mixer):
         kernels.conv_tokens(proj[:, inner : inner + C], self.conv_w, self.conv_b, state[:, : max(self.conv_elems, 1)],
                             xbc, ctx.q_start, ctx.q_len, ctx.seq_slots, ctx.num_seqs, T, kernels.ACT_SILU)
         y = ws.get(f"state_space.y{inner}", (ws.max_tokens, inner), torch.float32)
+        scratch = None
+        if T > ctx.num_seqs:
+            # Portions: long ones run in chunks of tokens side by side.
+            size = kernels.ssd_scan_scratch(ws.max_tokens, state.shape[0], self.heads, self.state_size, self.value_dim)
+            scratch = ws.get(f"state_space.chunks{self.heads}_{self.state_size}_{self.value_dim}", (size,), torch.float32)
         kernels.ssd_scan(xbc, proj[:, inner + C : inner + C + self.heads], self.dt_bias, self.a_log, self.d_skip,
                          state[:, self.conv_elems : self.conv_elems + self.state_elems], y, self.heads, self.groups,
-                         self.state_size, self.value_dim, ctx.q_start, ctx.q_len, ctx.seq_slots, ctx.num_seqs)
+                         self.state_size, self.value_dim, ctx.q_start, ctx.q_len, ctx.seq_slots, ctx.num_seqs,
+                         scratch=scratch, num_tokens=T)
         normed = ws.get(f"state_space.normed{inner}", (ws.max_tokens, inner), self.dtype)
         kernels.gated_group_norm(y, proj[:, :inner], self.norm_w, self.eps, self.norm_groups, normed, T)
         if ctx.residual is not None and self.dtype != torch.float32:
