@@ -419,7 +419,8 @@ class WindowAttentionConfig:
 
     def to_json_dict(self) -> Dict[str, Any]:
         mask: Dict[str, Any] = {"size": self.window}
-        if self.keep_first:
+        if self.keep_first or self.sink:
+            # the mixer beside a recurrence always names its kept keys, even none
             mask["keep_first"] = self.keep_first
         out: Dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim,
                                "scale": self.scale, "mask": mask}
