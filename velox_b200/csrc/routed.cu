@@ -447,7 +447,9 @@ VX_API int vx_table_experts_rows(const void* h, int dtype, long long h_stride, c
   if (num_tokens <= 0) return 0;
   const size_t smem_up = sizeof(float) * (size_t)width, smem_down = sizeof(float) * (size_t)top * ff;
   if (smem_up > 48 * 1024 || smem_down > 48 * 1024) return (int)cudaErrorInvalidValue;
-  const int rows_up = 32, rows_down = 32;
+  // Eight warps a block: four rows a warp of the first product, two of the second (whose rows are
+  // `top` dot products each), so that both grids have several blocks for every SM.
+  const int rows_up = 32, rows_down = 16;
   const dim3 grid_up((ff + rows_up - 1) / rows_up, num_tokens * top);
   const dim3 grid_down((width + rows_down - 1) / rows_down, num_tokens);
   if (dtype == VX_DTYPE_F32) {

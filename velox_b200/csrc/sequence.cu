@@ -368,14 +368,14 @@ constexpr int SSD_WARPS = 4;
 constexpr int SSD_CHUNK = 256;
 constexpr int SSD_SLICE = SSD_NS + 4;  // a lane's B (C) values in shared memory: padded against bank conflicts
 
-template <typename T, int RL>
+template <typename T, int RL, int MODE>
 __global__ void __launch_bounds__(SSD_WARPS * 32) ssd_scan_kernel(
     const float* __restrict__ xbc, long long xbc_stride, const T* __restrict__ dt_in, long long dt_stride,
     const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
     float* __restrict__ state, long long state_stride, float* __restrict__ y_out, long long y_stride, int heads,
     int groups, int N, int P, int col_blocks, const int* __restrict__ q_start, const int* __restrict__ q_len,
-    const int* __restrict__ seq_slots, int mode, float* __restrict__ chunk_states,
-    float* __restrict__ chunk_decay) {
+    const int* __restrict__ seq_slots, float* __restrict__ chunk_states, float* __restrict__ chunk_decay) {
+  constexpr int mode = MODE;
   extern __shared__ __align__(16) float ssd_s[];
   allow_dependents();
   grid_dependency_wait();
@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(SSD_WARPS * 32) ssd_scan_kernel(
       const int idx = tid + u * THREADS;
       const int arr = idx / (SSD_TC * NP), rem = idx - arr * (SSD_TC * NP);
       const int k = rem / NP, n = rem - k * NP;
-      pre_bc[u] = (k < tc && n < N)
+      pre_bc[u] = (k < tc && n < N && (mode != 1 || arr == 0))  // a pass that writes no y needs no C
                       ? xbc[(size_t)(start + i0 + k) * xbc_stride + inner + arr * groups * N + g * N + n]
                       : 0.f;
     }
@@ -475,15 +475,18 @@ __global__ void __launch_bounds__(SSD_WARPS * 32) ssd_scan_kernel(
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < SSD_NS / 4; ++j) {
-        const float4 bv = b4[j], cv = c4[j];
+        const float4 bv = b4[j];
+        const float4 cv = mode != 1 ? c4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
         S[4 * j] = fmaf(decay, S[4 * j], bv.x * xin);
         S[4 * j + 1] = fmaf(decay, S[4 * j + 1], bv.y * xin);
         S[4 * j + 2] = fmaf(decay, S[4 * j + 2], bv.z * xin);
         S[4 * j + 3] = fmaf(decay, S[4 * j + 3], bv.w * xin);
-        acc[0] = fmaf(S[4 * j], cv.x, acc[0]);
-        acc[1] = fmaf(S[4 * j + 1], cv.y, acc[1]);
-        acc[2] = fmaf(S[4 * j + 2], cv.z, acc[2]);
-        acc[3] = fmaf(S[4 * j + 3], cv.w, acc[3]);
+        if (mode != 1) {
+          acc[0] = fmaf(S[4 * j], cv.x, acc[0]);
+          acc[1] = fmaf(S[4 * j + 1], cv.y, acc[1]);
+          acc[2] = fmaf(S[4 * j + 2], cv.z, acc[2]);
+          acc[3] = fmaf(S[4 * j + 3], cv.w, acc[3]);
+        }
       }
       if (mode != 1) {
         float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
@@ -714,8 +717,23 @@ VX_API int vx_rglru_gates(const float* u, long long u_stride, int width, int blo
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     launch_pdl(rglru_gates_kernel<TT>, dim3((num_tokens + TT - 1) / TT, blocks), dim3(threads), smem, stream, u,
                u_stride, part, wa_t, ba, wi_t, bi, lam, decay_scale, a_out, b_out, ab_stride, num_tokens);
-  } else {
+  } else if (num_tokens < 128 || (size_t)32 * part * sizeof(float) > 200 * 1024) {
     constexpr int TT = 16;
+    const size_t smem = sizeof(float) * TT * part;
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+      cudaError_t e = cudaFuncSetAttribute(rglru_gates_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      configured = smem;
+    }
+    launch_pdl(rglru_gates_kernel<TT>, dim3((num_tokens + TT - 1) / TT, blocks), dim3(threads), smem, stream, u,
+               u_stride, part, wa_t, ba, wi_t, bi, lam, decay_scale, a_out, b_out, ab_stride, num_tokens);
+  } else {
+    // Long steps: 32 tokens a block, so that a block's pass over the two matrices (read from the
+    // L2 by every block) serves twice the tokens.
+    constexpr int TT = 32;
     const size_t smem = sizeof(float) * TT * part;
     static size_t configured = 48 * 1024;
     if (smem > configured) {
@@ -771,32 +789,36 @@ static int launch_ssd(const float* xbc, long long xbc_stride, const void* dt_in,
   const size_t smem = sizeof(float) * 2 * ((size_t)2 * SSD_TC * RL * SSD_SLICE + (size_t)SSD_TC * COLS + 2 * SSD_TC);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<T, RL, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(ssd_scan_kernel<T, RL, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(ssd_scan_kernel<T, RL, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
   const dim3 block(SSD_WARPS * 32);
   if (scratch == nullptr || num_tokens <= SSD_CHUNK) {
-    launch_pdl(ssd_scan_kernel<T, RL>, dim3(heads * col_blocks, num_seqs), block, smem, stream, xbc, xbc_stride,
+    launch_pdl(ssd_scan_kernel<T, RL, 0>, dim3(heads * col_blocks, num_seqs), block, smem, stream, xbc, xbc_stride,
                (const T*)dt_in, dt_stride, dt_bias, a_log, d_skip, state, state_stride, y_out, y_stride, heads, groups,
-               N, P, col_blocks, q_start, q_len, seq_slots, 0, (float*)nullptr, (float*)nullptr);
+               N, P, col_blocks, q_start, q_len, seq_slots, (float*)nullptr, (float*)nullptr);
     return (int)cudaGetLastError();
   }
   const size_t places = (size_t)(num_tokens / SSD_CHUNK + num_seqs + 1);
   float* chunk_states = scratch;
   float* chunk_decay = scratch + places * heads * N * P;
   const dim3 grid(heads * col_blocks, num_seqs, (num_tokens + SSD_CHUNK - 1) / SSD_CHUNK);
-  launch_pdl(ssd_scan_kernel<T, RL>, grid, block, smem, stream, xbc, xbc_stride, (const T*)dt_in, dt_stride, dt_bias,
+  launch_pdl(ssd_scan_kernel<T, RL, 1>, grid, block, smem, stream, xbc, xbc_stride, (const T*)dt_in, dt_stride, dt_bias,
              a_log, d_skip, state, state_stride, y_out, y_stride, heads, groups, N, P, col_blocks, q_start, q_len,
-             seq_slots, 1, chunk_states, chunk_decay);
+             seq_slots, chunk_states, chunk_decay);
   const int per_head = N * P;
   int cblocks = (int)(((size_t)heads * per_head + 255) / 256);
   if (cblocks > 148 * 4) cblocks = 148 * 4;
   launch_pdl(ssd_combine_kernel, dim3(cblocks, num_seqs), dim3(256), 0, stream, state, state_stride, chunk_states,
              (const float*)chunk_decay, heads, per_head, q_start, q_len, seq_slots);
-  launch_pdl(ssd_scan_kernel<T, RL>, grid, block, smem, stream, xbc, xbc_stride, (const T*)dt_in, dt_stride, dt_bias,
+  launch_pdl(ssd_scan_kernel<T, RL, 2>, grid, block, smem, stream, xbc, xbc_stride, (const T*)dt_in, dt_stride, dt_bias,
              a_log, d_skip, state, state_stride, y_out, y_stride, heads, groups, N, P, col_blocks, q_start, q_len,
-             seq_slots, 2, chunk_states, chunk_decay);
+             seq_slots, chunk_states, chunk_decay);
   return (int)cudaGetLastError();
 }
 
