@@ -75,6 +75,9 @@ def test_named_model_sizes_are_configurations_of_the_architecture():
         if name.startswith("peratar-") or name == "tiny-p":
             assert arch.name == "Peratar" and typed.num_hidden_layers == len(cfg["layers"])
             continue
+        if name.startswith("redalix-") or name == "tiny-r":
+            assert arch.name == "Redalix" and typed.num_hidden_layers == len(cfg["layers"])
+            continue
         assert arch.name == "Qwen2ForCausalLM"
         c = Qwen2Config.from_dict(cfg)
         assert c.num_attention_heads % c.num_key_value_heads == 0
