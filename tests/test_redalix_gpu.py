@@ -340,6 +340,40 @@ def test_experts_grouped_many_tokens(tokens, width, ff, experts, top):
     close(resid, want.cpu().numpy(), "float32", "grouped experts", scale=float(want.abs().max()) * 300)
 
 
+@pytest.mark.parametrize("tokens,width,ff,experts,top", [(500, 128, 96, 6, 2), (300, 256, 64, 9, 3), (1100, 64, 32, 4, 1)])
+def test_experts_with_the_library_grouped_product(tokens, width, ff, experts, top):
+    """The long-step form whose two products are the library's grouped product, around this
+    package's ordering, gather, activation and sum; an expert nobody names has an empty run."""
+    from velox_b200.ops import kernels
+
+    if not kernels.has_library_grouped_product():
+        pytest.skip("this torch has no grouped product")
+    gen = torch.Generator().manual_seed(tokens + 1)
+    vocab = 40
+    h = torch.randn(tokens, width + 8, generator=gen).to(torch.bfloat16).cuda()
+    up = (torch.randn(experts, ff, width, generator=gen) / width ** 0.5).to(torch.bfloat16).cuda()
+    down = (torch.randn(experts, width, ff, generator=gen) / ff ** 0.5).to(torch.bfloat16).cuda()
+    table = (1 + torch.rand(vocab, experts - 1, generator=gen).argsort(dim=1)[:, :top]).to(torch.int32).contiguous().cuda()
+    ids = torch.randint(0, vocab, (tokens,), generator=gen).to(torch.int32).cuda()
+    resid = torch.randn(tokens, width, generator=gen).cuda()
+    want = resid.double()
+    chosen = table[ids.long()].long()
+    x = h[:, 8:]
+    for k in range(top):
+        a = torch.relu(torch.einsum("tw,tfw->tf", x.double(), up.double()[chosen[:, k]]).to(torch.bfloat16).double()) ** 2
+        want = want + torch.einsum("tf,twf->tw", a.to(torch.bfloat16).double(), down.double()[chosen[:, k]]) / top
+    places = kernels.grouped_places(tokens, top, experts)
+    route = torch.zeros(2 * places + tokens * top, dtype=torch.int32).cuda()
+    ends = torch.zeros(experts, dtype=torch.int32).cuda()
+    a_rows = torch.zeros(places, width, dtype=torch.bfloat16).cuda()
+    status = torch.zeros(4, dtype=torch.int32).cuda()
+    assert kernels.table_experts_library(x, ids, None, table, up, down, route, ends, a_rows, resid, tokens, status)
+    assert int(status[0]) == 0
+    assert int(ends[0]) == 0 and int(ends[-1]) <= places
+    close(resid, want.cpu().numpy(), "float32", "experts through the library's grouped product",
+          scale=float(want.abs().max()) * 3000)
+
+
 @pytest.mark.parametrize("dtype", list(DTYPES))
 def test_pair_rotation_cache_write_and_head_gate(dtype):
     from velox_b200.ops import kernels

@@ -209,7 +209,8 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 __global__ void route_pairs_kernel(const int* __restrict__ ids, const int* __restrict__ fed, int num_fed,
                                    const int* __restrict__ table, int vocab, int top, int experts, int num_tokens,
                                    int capacity, int max_tiles, int* __restrict__ tile_expert,
-                                   int* __restrict__ place_token, int* __restrict__ pair_place, int* status) {
+                                   int* __restrict__ place_token, int* __restrict__ pair_place, int* status,
+                                   int* __restrict__ run_ends) {
   extern __shared__ int route_s[];  // counts [experts], starts [experts], cursor [experts]
   int* counts = route_s;
   int* starts = counts + experts;
@@ -241,6 +242,7 @@ __global__ void route_pairs_kernel(const int* __restrict__ ids, const int* __res
       const int tiles = (counts[e] + GG_M - 1) / GG_M;
       for (int i = 0; i < tiles; ++i) tile_expert[at / GG_M + i] = e;
       at += tiles * GG_M;
+      if (run_ends != nullptr) run_ends[e] = at;  // where the expert's (padded) run ends
     }
   }
   __syncthreads();
@@ -385,7 +387,25 @@ __global__ void __launch_bounds__(128) grouped_gemm_kernel(
     }
 }
 
-__global__ void gather_pairs_kernel(const float* __restrict__ rows, long long row_stride,
+// rows[place, :] = h[token of the place, :], zeros for padding places (16-byte chunks).
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ h, long long h_stride,
+                                   const int* __restrict__ place_token, int chunks, long long total,
+                                   __nv_bfloat16* __restrict__ rows) {
+  allow_dependents();
+  grid_dependency_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long place = idx / chunks;
+    const int c = (int)(idx - place * chunks) * 8;
+    const int token = place_token[place];
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (token >= 0) v = *reinterpret_cast<const uint4*>(h + (size_t)token * h_stride + c);
+    *reinterpret_cast<uint4*>(rows + (size_t)place * chunks * 8 + c) = v;
+  }
+}
+
+template <typename R>
+__global__ void gather_pairs_kernel(const R* __restrict__ rows, long long row_stride,
                                     const int* __restrict__ pair_place, int top, int width,
                                     float* __restrict__ resid) {
   allow_dependents();
@@ -396,7 +416,7 @@ __global__ void gather_pairs_kernel(const float* __restrict__ rows, long long ro
     float sum = 0.f;
     for (int k = 0; k < top; ++k) {
       const int place = pair_place[t * top + k];
-      if (place >= 0) sum += rows[(size_t)place * row_stride + i];
+      if (place >= 0) sum += to_float(rows[(size_t)place * row_stride + i]);
     }
     resid[(size_t)t * width + i] += sum * scale;
   }
@@ -489,7 +509,7 @@ VX_API int vx_table_experts_grouped(const void* h, long long h_stride, const int
   const size_t smem = sizeof(int) * 3 * (size_t)experts;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   launch_pdl(route_pairs_kernel, dim3(1), dim3(1024), smem, stream, ids, fed, num_fed, table, vocab, top, experts,
-             num_tokens, capacity, max_tiles, tile_expert, place_token, pair_place, status);
+             num_tokens, capacity, max_tiles, tile_expert, place_token, pair_place, status, (int*)nullptr);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -506,7 +526,81 @@ VX_API int vx_table_experts_grouped(const void* h, long long h_stride, const int
   launch_pdl(grouped_gemm_kernel<false>, dim3(max_tiles, (width + GG_N - 1) / GG_N), dim3(128), GG_SMEM_BYTES, stream,
              (const __nv_bfloat16*)act, act_stride, (const int*)place_token, (const int*)tile_expert,
              (const __nv_bfloat16*)w_down, width, ff, (__nv_bfloat16*)nullptr, rows, (long long)width);
-  launch_pdl(gather_pairs_kernel, dim3(num_tokens), dim3(256), 0, stream, (const float*)rows, (long long)width,
+  launch_pdl(gather_pairs_kernel<float>, dim3(num_tokens), dim3(256), 0, stream, (const float*)rows, (long long)width,
              (const int*)pair_place, top, width, resid);
+  return (int)cudaGetLastError();
+}
+
+// The same for bfloat16 rows of whole 16-byte chunks: eight values a thread.
+__global__ void gather_pairs_vec_kernel(const __nv_bfloat16* __restrict__ rows, long long row_stride,
+                                        const int* __restrict__ pair_place, int top, int width,
+                                        float* __restrict__ resid) {
+  allow_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const float scale = 1.0f / (float)top;
+  for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k) {
+      const int place = pair_place[t * top + k];
+      if (place < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(rows + (size_t)place * row_stride + i);
+      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = __bfloat1622float2(pairs[q]);
+        sum[2 * q] += f.x;
+        sum[2 * q + 1] += f.y;
+      }
+    }
+    float4* out = reinterpret_cast<float4*>(resid + (size_t)t * width + i);
+    float4 a = out[0], b = out[1];
+    a.x += sum[0] * scale; a.y += sum[1] * scale; a.z += sum[2] * scale; a.w += sum[3] * scale;
+    b.x += sum[4] * scale; b.y += sum[5] * scale; b.z += sum[6] * scale; b.w += sum[7] * scale;
+    out[0] = a;
+    out[1] = b;
+  }
+}
+
+// The routing alone, for a caller that runs the two products as a library's grouped product: the
+// places as above, run_ends [experts] (where each expert's padded run ends), and the rows of h
+// gathered by place into a_rows [capacity, width] (bfloat16).
+VX_API int vx_route_and_gather(const void* h, long long h_stride, const int* ids, const int* fed, int num_fed,
+                               const int* table, int vocab, int top, int experts, int width, int* route,
+                               int capacity, int* run_ends, void* a_rows, int num_tokens, int* status,
+                               cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (capacity % GG_M != 0 || capacity < num_tokens * top + experts * (GG_M - 1)) return (int)cudaErrorInvalidValue;
+  if ((width & 7) != 0 || (h_stride & 7) != 0) return (int)cudaErrorInvalidValue;
+  const int max_tiles = capacity / GG_M;
+  int* tile_expert = route;
+  int* place_token = route + max_tiles;
+  int* pair_place = place_token + capacity;
+  const size_t smem = sizeof(int) * 3 * (size_t)experts;
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  launch_pdl(route_pairs_kernel, dim3(1), dim3(1024), smem, stream, ids, fed, num_fed, table, vocab, top, experts,
+             num_tokens, capacity, max_tiles, tile_expert, place_token, pair_place, status, run_ends);
+  const long long total = (long long)capacity * (width / 8);
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_pdl(gather_rows_kernel, dim3((int)blocks), dim3(256), 0, stream, (const __nv_bfloat16*)h, h_stride,
+             (const int*)place_token, width / 8, total, (__nv_bfloat16*)a_rows);
+  return (int)cudaGetLastError();
+}
+
+// resid[t] += (sum over the token's pairs, in their order, of rows[place of the pair]) / top;
+// rows bfloat16 [capacity, width]; route as written by vx_route_and_gather.
+VX_API int vx_gather_pairs(const void* rows, const int* route, int capacity, int top, int width, float* resid,
+                           int num_tokens, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int* pair_place = route + capacity / GG_M + capacity;
+  if ((width & 7) == 0 && (reinterpret_cast<uintptr_t>(rows) & 15) == 0 && (reinterpret_cast<uintptr_t>(resid) & 15) == 0) {
+    const int threads = width / 8 >= 256 ? 256 : (width / 8 + 31) / 32 * 32;
+    launch_pdl(gather_pairs_vec_kernel, dim3(num_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)rows,
+               (long long)width, pair_place, top, width, resid);
+    return (int)cudaGetLastError();
+  }
+  launch_pdl(gather_pairs_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)rows,
+             (long long)width, pair_place, top, width, resid);
   return (int)cudaGetLastError();
 }

@@ -157,6 +157,11 @@ def mixers():
             _ptr, _c_ll, _ptr, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _c_int, _ptr, _c_int,
             _ptr, _c_ll, _ptr, _ptr, _c_int, _ptr, _ptr,
         ]
+        lib.vx_route_and_gather.argtypes = [
+            _ptr, _c_ll, _ptr, _ptr, _c_int, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _c_int,
+            _ptr, _ptr,
+        ]
+        lib.vx_gather_pairs.argtypes = [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
         _mixers = lib
     return _mixers
 
@@ -1474,4 +1479,45 @@ def table_experts_grouped(h, ids, fed, table, w_up, w_down, route, act, rows, re
                                           places, _p(act), ff, _p(rows), _p(resid), num_tokens, _p(status), _stream()),
         "table_experts_grouped",
     )
+    return True
+
+
+def has_library_grouped_product() -> bool:
+    """Whether torch offers a grouped matrix product with the groups' ends on the device."""
+    return hasattr(torch, "_grouped_mm")
+
+
+def table_experts_library(h, ids, fed, table, w_up, w_down, route, run_ends, a_rows, resid, num_tokens, status) -> bool:
+    """``table_experts`` for long bfloat16 steps with the two products as the library's grouped
+    product (one launch each over all experts, the runs' ends read on the device): this
+    package's kernels order the pairs by expert and gather the rows (``vx_route_and_gather``),
+    square the positive parts, and sum a token's pairs into the stream.  ``route`` int32 scratch
+    as for ``table_experts_grouped``, ``run_ends`` int32 [experts], ``a_rows`` bfloat16
+    [places, width].  False: sizes it does not take, or no such product in this torch."""
+    experts, ff, width = w_up.shape
+    vocab, top = table.shape
+    if (not has_library_grouped_product() or h.dtype != torch.bfloat16 or width % 16 or ff % 16
+            or _pitched(h, "h") % 8 or experts * 12 > 48 * 1024):
+        return False
+    places = grouped_places(num_tokens, top, experts)
+    tile = int(mixers().vx_grouped_tile_rows())
+    if route.numel() < places // tile + places + num_tokens * top or a_rows.shape[0] < places or a_rows.shape[1] != width:
+        raise ValueError("table_experts_library: the scratch buffers are too small")
+    _need(route, torch.int32, "route")
+    _need(run_ends, torch.int32, "run_ends")
+    _need(a_rows, torch.bfloat16, "a_rows")
+    _need(resid, torch.float32, "resid")
+    _check(
+        mixers().vx_route_and_gather(_p(h), _pitched(h, "h"), _p(ids), _p(fed), 0 if fed is None else fed.numel(),
+                                     _p(table), vocab, top, experts, width, _p(route), places, _p(run_ends),
+                                     _p(a_rows), num_tokens, _p(status), _stream()),
+        "route_and_gather",
+    )
+    up = torch._grouped_mm(a_rows[:places], w_up.transpose(1, 2), offs=run_ends)
+    note_library_launch("library_grouped_gemm")
+    act_rows(up, up, places, ACT_RELU_SQUARED)
+    down = torch._grouped_mm(up, w_down.transpose(1, 2), offs=run_ends)
+    note_library_launch("library_grouped_gemm")
+    _check(mixers().vx_gather_pairs(_p(down), _p(route), places, top, width, _p(resid), num_tokens, _stream()),
+           "gather_pairs")
     return True

@@ -15,6 +15,10 @@ from .base import FeedForward, PendingSums
 from .registry import register_part
 
 
+# VELOX_B200_NO_LIBRARY_GROUPED=1 keeps the experts of long steps on this package's own tiled
+# kernel (for comparison, and for a torch without a grouped product).
+_LIBRARY_GROUPED = os.environ.get("VELOX_B200_NO_LIBRARY_GROUPED") != "1"
+
 # VELOX_B200_NO_MLP_FUSION=1 keeps the two projections of a small step as kernels of their own
 # (for bisecting; the fused kernel's sum over the inner width has no fixed order).
 _FUSE_MLP = os.environ.get("VELOX_B200_NO_MLP_FUSION") != "1" and not DETERMINISTIC
@@ -248,11 +252,24 @@ class TableExperts(FeedForward):
     # (token, expert) pairs ordered by expert; shorter ones as matrix-vector products spread over
     # the grid (every pair then reads its expert's matrices once).
     GROUPED_FROM_TOKENS = 48
+    # ... and beyond the projections' small-step limit as the library's grouped product (one launch
+    # over all experts, the runs' ends read on the device), where torch has one.
+    LIBRARY_FROM_TOKENS = 256
 
     def _experts(self, x, ctx, target, T) -> None:
         ws = ctx.workspace
         ids, fed = ctx.token_ids, getattr(ctx, "fed_tokens", None)
         X, F, E = self.experts, self.expert_ff, self.hidden_size
+        if self.dtype == torch.bfloat16 and T > self.LIBRARY_FROM_TOKENS and _LIBRARY_GROUPED:
+            # Long steps: the projections' rule (library products beyond the small-step limit).
+            places = kernels.grouped_places(T, self.top, X)
+            most = kernels.grouped_places(ws.max_tokens, self.top, X)
+            route = ws.get(f"table_experts.route{most}", (2 * most + ws.max_tokens * self.top,), torch.int32)
+            ends = ws.get(f"table_experts.ends{X}", (X,), torch.int32)
+            a_rows = ws.get(f"table_experts.gathered{E}", (most, E), torch.bfloat16)
+            if kernels.table_experts_library(x, ids, fed, self.table, self.w_up, self.w_down, route, ends,
+                                             a_rows[:places], target, T, ctx.status):
+                return
         if self.dtype == torch.bfloat16 and T > self.GROUPED_FROM_TOKENS:
             places = kernels.grouped_places(ws.max_tokens, self.top, X)
             route = ws.get(f"table_experts.route{places}", (2 * places + ws.max_tokens * self.top,), torch.int32)
