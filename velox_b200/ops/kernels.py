@@ -1482,9 +1482,13 @@ def table_experts_grouped(h, ids, fed, table, w_up, w_down, route, act, rows, re
     return True
 
 
+_library_grouped_refused = False
+
+
 def has_library_grouped_product() -> bool:
-    """Whether torch offers a grouped matrix product with the groups' ends on the device."""
-    return hasattr(torch, "_grouped_mm")
+    """Whether torch offers a grouped matrix product with the groups' ends on the device (and
+    has not refused a call of this process)."""
+    return hasattr(torch, "_grouped_mm") and not _library_grouped_refused
 
 
 def table_experts_library(h, ids, fed, table, w_up, w_down, route, run_ends, a_rows, resid, num_tokens, status) -> bool:
@@ -1513,11 +1517,18 @@ def table_experts_library(h, ids, fed, table, w_up, w_down, route, run_ends, a_r
                                      _p(a_rows), num_tokens, _p(status), _stream()),
         "route_and_gather",
     )
-    up = torch._grouped_mm(a_rows[:places], w_up.transpose(1, 2), offs=run_ends)
-    note_library_launch("library_grouped_gemm")
-    act_rows(up, up, places, ACT_RELU_SQUARED)
-    down = torch._grouped_mm(up, w_down.transpose(1, 2), offs=run_ends)
-    note_library_launch("library_grouped_gemm")
+    global _library_grouped_refused
+    try:
+        up = torch._grouped_mm(a_rows[:places], w_up.transpose(1, 2), offs=run_ends)
+        note_library_launch("library_grouped_gemm")
+        act_rows(up, up, places, ACT_RELU_SQUARED)
+        down = torch._grouped_mm(up, w_down.transpose(1, 2), offs=run_ends)
+        note_library_launch("library_grouped_gemm")
+    except (RuntimeError, TypeError, ValueError, NotImplementedError):
+        # The library does not take these sizes (or this build has no kernel for them): nothing
+        # has been added to the stream yet, and the caller's own kernels take over for good.
+        _library_grouped_refused = True
+        return False
     _check(mixers().vx_gather_pairs(_p(down), _p(route), places, top, width, _p(resid), num_tokens, _stream()),
            "gather_pairs")
     return True
